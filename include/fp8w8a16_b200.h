@@ -1,0 +1,136 @@
+/* C ABI of the B200 (sm_100a) block-scaled FP8 W8A16 linear / MoE engine.
+ *
+ * Plain pointers and sizes only: every pointer is a DEVICE pointer unless it says "host"; `stream`
+ * is a cudaStream_t passed as void* (NULL = the legacy default stream; callers inside PyTorch pass
+ * torch.cuda.current_stream().cuda_stream — the reference launches on the current torch stream,
+ * src/fp8_w8a16_sm70/fp8_dequant.cu:29-36, and so must every caller of this library).
+ * Every function returns 0 or a negative FP8W8A16_ERR_* code; fp8w8a16_last_error() gives the
+ * message of the calling thread's last failure (the reference raises through TORCH_CHECK,
+ * fp8_dequant.cu:1518-1537; the Python binding turns a non-zero code into RuntimeError).
+ * No function allocates device memory or synchronises with the host unless it says so.
+ *
+ * Layouts (the reference's; see the signatures at fp8_dequant.cu:1616-1622):
+ *   x       FP16 [M, K] row-major          w   uint8 (raw E4M3-FN) [N, K] row-major, or [E, N, K]
+ *   scales  [ceil(N/block_h), ceil(K/128)] (or [E, ., .]), FP16 or fp32 (rounded to FP16 on use),
+ *           block_h = 128 (block scales) or 1 (per-output-channel "fake block" grid)
+ *   out     FP16 [M, N] row-major, fp32 accumulation
+ */
+#ifndef FP8W8A16_B200_H_
+#define FP8W8A16_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FP8W8A16_OK 0
+#define FP8W8A16_ERR_INVALID (-1)     /* bad argument: null pointer, negative size, misalignment */
+#define FP8W8A16_ERR_CUDA (-2)        /* a CUDA runtime / driver call failed */
+#define FP8W8A16_ERR_UNSUPPORTED (-3) /* shape or block size outside what the kernels cover */
+#define FP8W8A16_ERR_WORKSPACE (-4)   /* workspace missing or too small */
+#define FP8W8A16_ERR_DEVICE (-5)      /* a kernel reported a timed-out wait in the device status word */
+
+#define FP8W8A16_SCALE_F16 0
+#define FP8W8A16_SCALE_F32 1
+
+#define FP8W8A16_DTYPE_F32 0
+#define FP8W8A16_DTYPE_F16 1
+#define FP8W8A16_DTYPE_BF16 2
+
+/* fp8w8a16_linear `algo` */
+#define FP8W8A16_ALGO_AUTO 0 /* by M, as the reference's _v100_fp8_gemm dispatch does (vllm_serve.py:1032-1100) */
+#define FP8W8A16_ALGO_GEMV 1 /* CUDA-core split-K GEMV, any M (weights re-streamed per 4 tokens) */
+#define FP8W8A16_ALGO_TC 2   /* tcgen05 tensor-core GEMM with in-SM dequant */
+
+int fp8w8a16_version(void);
+const char* fp8w8a16_last_error(void);
+
+/* Sticky device status word (bit set = a bounded wait inside a kernel gave up).  Synchronises the
+ * device.  *status (host) receives the bits; reset != 0 clears them. */
+int fp8w8a16_device_status(int* status, int reset);
+
+/* out[i] = cvt(w[i]).  Replaces fp8_e4m3_to_fp16 (fp8_dequant.cu:129-148). */
+int fp8w8a16_e4m3_to_fp16(const uint8_t* w, uint16_t* out, int64_t n, void* stream);
+
+/* out[i] = cvt(w[i]) * scales_f16[i / group_size].  Replaces fp8_e4m3_to_fp16_scaled (fp8_dequant.cu:150-199). */
+int fp8w8a16_e4m3_to_fp16_scaled(const uint8_t* w, const uint16_t* scales_f16, uint16_t* out, int64_t n,
+                                 int64_t group_size, void* stream);
+
+/* out[i,j] = RN16(cvt(w[i,j]) * S16[i/block_h, j/block_w]): the bit-exact dequantised weight.
+ * Replaces fp8_e4m3_to_fp16_block_scaled (fp8_dequant.cu:3053-3087). */
+int fp8w8a16_dequant_block_scaled(const uint8_t* w, const void* scales, int scale_dtype, uint16_t* out, int N, int K,
+                                  int block_h, int block_w, void* stream);
+
+/* Bytes of workspace fp8w8a16_linear may use for this shape (always >= 64 KiB: the first 64 KiB
+ * hold hand-off counters that must be ZERO before the first call and are left at zero by every
+ * call; the rest needs no initialisation).  One workspace serves one stream at a time. */
+size_t fp8w8a16_linear_workspace_bytes(int M, int N, int K);
+
+/* out[M,N] = x[M,K] @ dequant(w[N,K], scales)^T.  One entry point for the reference's whole dense
+ * family — gemv_coalesced / gemv_coalesced_m / gemm_a1 / a2 / a3 / gemm_wmma_poc
+ * (fp8_dequant.cu:2769, 1616, 2969, 2925, 2717, 2114) — and for the host dispatch that picks among
+ * them (vllm_serve.py:1032-1100).  block_w must be 128, block_h 128 or 1, K a multiple of 16. */
+int fp8w8a16_linear(const uint16_t* x, const uint8_t* w, const void* scales, int scale_dtype, uint16_t* out, int M,
+                    int N, int K, int block_h, int block_w, int algo, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/* Router: logits [M,E] -> topk_ids int32 [M,topk] (descending, ties to the lowest expert id),
+ * topk_weights fp32 [M,topk] = softmax probabilities of the picks (renormalize != 0: divided by
+ * their sum).  Stands in for vLLM's fused_topk, whose output the reference's MoE apply consumes
+ * (vllm_serve.py:2175). */
+int fp8w8a16_moe_topk_softmax(const void* logits, int logits_dtype, int M, int E, int topk, int renormalize,
+                              int32_t* topk_ids, float* topk_weights, void* stream);
+
+/* Route table, built on the device without host synchronisation.  topk_ids: R routed slots, int32
+ * or int64 (ids_are_i64).  expert_map: optional int32 [n_global_experts] global -> local id, -1 =
+ * not on this rank (vllm_serve.py:2237-2243); ids < 0 or unmapped are dropped (they contribute
+ * zero).  Outputs: counts [E], offsets [E+1] (first sorted row per expert), tile_offsets [E+1]
+ * (prefix sum of ceil(count / token_tile)), sorted_route [R] (route index per sorted row, stable,
+ * -1 past the valid rows), inv_pos [R] (sorted row per route, -1 = dropped).
+ * Replaces the argsort / scatter_add / cumsum table of compressed_tensors_v100.py:776-784. */
+int fp8w8a16_moe_align(const void* topk_ids, int ids_are_i64, int R, const int32_t* expert_map, int n_global_experts,
+                       int num_local_experts, int token_tile, int32_t* counts, int32_t* offsets, int32_t* tile_offsets,
+                       int32_t* sorted_route, int32_t* inv_pos, void* stream);
+
+/* Token tile (16..256) the grouped GEMM uses for R routed rows over E experts. */
+int fp8w8a16_moe_token_tile(int R, int num_local_experts);
+
+/* Grouped expert GEMM over expert-sorted rows:
+ *   paired == 0: out[r, n] = (x_sorted[r] . dequant(w[e(r), n])) * row_weight[r]      (row_weight may be NULL)
+ *   paired != 0: w is a fused [E, 2N, K] gate/up weight; out[r, n] = silu(gate) * up  (FP16 rounding as the reference)
+ * offsets / tile_offsets come from fp8w8a16_moe_align with the same token_tile.
+ * Replaces fp8_w8a16_grouped_gemv_coalesced / grouped_routed_gemm_a3 / grouped_tiled_gemm
+ * (fp8_dequant.cu:1512, 2813, 3166) and TurboMind's fp8_moe_gemm_sm70_out
+ * (third_party/turbomind_gemm_sm70/binding/awq_sm70_gemm.cu:2327-2474). */
+int fp8w8a16_moe_grouped_gemm(const uint16_t* x_sorted, const uint8_t* w, const void* scales, int scale_dtype,
+                              uint16_t* out, const float* row_weight, const int32_t* offsets,
+                              const int32_t* tile_offsets, int R, int num_local_experts, int N, int K, int block_h,
+                              int paired, int token_tile, void* workspace, size_t workspace_bytes, void* stream);
+size_t fp8w8a16_moe_grouped_gemm_workspace_bytes(int R, int num_local_experts, int N, int K, int paired,
+                                                 int token_tile);
+
+/* Whole routed MoE layer (routed-only output, as the reference's apply returns, vllm_serve.py:2175-2411):
+ *   out[m] = sum_j w[m,j] * down_e( silu(gate_e x[m]) * up_e x[m] ),  e = topk_ids[m,j]
+ * x FP16 [M,H]; topk_weights fp32 [M,topk]; w13 [E,2I,H], w2 [E,H,I] E4M3; scales as above with
+ * block_h 128 or 1.  weight_on_input: multiply x by the route weight instead of the output
+ * (apply_router_weight_on_input, vllm_serve.py:1868).  Steps: align -> gather -> grouped w13 with
+ * fused SiLU*mul -> grouped w2 with fused route weight -> combine; no host synchronisation. */
+int fp8w8a16_moe_forward(const uint16_t* x, const void* topk_ids, int ids_are_i64, const float* topk_weights,
+                         const int32_t* expert_map, int n_global_experts, const uint8_t* w13, const void* s13,
+                         const uint8_t* w2, const void* s2, int scale_dtype, uint16_t* out, int M, int topk,
+                         int num_local_experts, int H, int I, int block_h, int weight_on_input, void* workspace,
+                         size_t workspace_bytes, void* stream);
+size_t fp8w8a16_moe_workspace_bytes(int M, int topk, int num_local_experts, int H, int I);
+
+/* Pieces of the layer, exported so each can be checked on its own. */
+int fp8w8a16_moe_gather(const uint16_t* x, const int32_t* sorted_route, const float* topk_weights, int R, int topk,
+                        int H, int weight_on_input, uint16_t* x_sorted, float* w_sorted, void* stream);
+int fp8w8a16_moe_combine(const uint16_t* y_sorted, const int32_t* inv_pos, int M, int topk, int H, uint16_t* out,
+                         void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FP8W8A16_B200_H_ */

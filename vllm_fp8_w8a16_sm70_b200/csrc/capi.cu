@@ -1,0 +1,443 @@
+// C-ABI entry points (include/fp8w8a16_b200.h): argument validation, algorithm choice, workspace
+// carve-up and kernel launches.  No allocation, no host synchronisation (except device_status).
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "gemm_tc.h"
+
+namespace w8a16 {
+
+// ---- error plumbing ------------------------------------------------------------------------------
+static thread_local char t_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_err, sizeof(t_err), fmt, ap);
+    va_end(ap);
+}
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(t_err, sizeof(t_err), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int sm_count() {
+    static int cached[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+// ---- kernels defined in the other translation units -------------------------------------------------
+int launch_e4m3_to_fp16(const uint8_t* in, __half* out, int64_t n, cudaStream_t st);
+int launch_e4m3_to_fp16_scaled(const uint8_t* in, const __half* scales, __half* out, int64_t n, int64_t group, cudaStream_t st);
+int launch_dequant_block(const uint8_t* w, const void* scales, int scale_dtype, __half* out, int N, int K, int block_h,
+                         int block_w, cudaStream_t st);
+size_t gemv_workspace_bytes(int M, int N, int K);
+int launch_gemv(const __half* x, const uint8_t* w, const void* scales, int scale_dtype, __half* out, int M, int N, int K,
+                int block_h, int block_w, void* workspace, size_t workspace_bytes, cudaStream_t st);
+int launch_topk_softmax(const void* logits, int logits_dtype, int M, int E, int topk, int renorm, int* ids, float* weights,
+                        cudaStream_t st);
+int launch_align(const void* ids, int ids_are_i64, int R, const int* expert_map, int n_global, int E, int bt, int* counts,
+                 int* offsets, int* tile_offsets, int* sorted_route, int* inv_pos, cudaStream_t st);
+int launch_gather(const __half* x, const int* sorted_route, const float* topk_w, int R, int topk, int H, int weight_on_input,
+                  __half* x_sorted, float* w_sorted, cudaStream_t st);
+int launch_combine(const __half* y_sorted, const int* inv_pos, int M, int topk, int H, __half* out, cudaStream_t st);
+
+namespace {
+
+inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
+
+// Number of K splits for `tiles` output tiles of `total_kb` K blocks each: the smallest split count
+// that fills at least 85 % of the last wave of SMs, leaving every split at least two K blocks.
+int pick_splits(int tiles, int total_kb) {
+    const int sms = sm_count();
+    if (tiles >= sms || total_kb < 4) return 1;
+    int max_s = total_kb / 2;
+    if (max_s > 16) max_s = 16;
+    int best = 1;
+    double best_eff = 0.0;
+    for (int s = 1; s <= max_s; ++s) {
+        const int units = tiles * s;
+        const int waves = (units + sms - 1) / sms;
+        const double eff = (double)units / ((double)sms * waves);
+        if (eff > best_eff + 1e-9) {
+            best_eff = eff;
+            best = s;
+        }
+        if (eff >= 0.85) return s;
+    }
+    return best;
+}
+
+struct SplitPlan {
+    int splits;
+    int kb_per_split;
+};
+
+SplitPlan plan_splits(int tiles_for_heuristic, int tiles_upper_bound, int K, int bk) {
+    const int total_kb = (K + bk - 1) / bk;
+    int s = pick_splits(tiles_for_heuristic, total_kb);
+    if ((size_t)tiles_upper_bound * sizeof(unsigned int) > kTicketBytes) s = 1;
+    SplitPlan sp;
+    sp.kb_per_split = (total_kb + s - 1) / s;
+    sp.splits = (total_kb + sp.kb_per_split - 1) / sp.kb_per_split;
+    return sp;
+}
+
+size_t tc_dense_workspace_bytes(int M, int N, int K) {
+    const int bt = tc_pick_bt(M), bk = tc_block_k(bt, false);
+    const int tiles = ((N + 127) / 128) * ((M + bt - 1) / bt);
+    const SplitPlan sp = plan_splits(tiles, tiles, K, bk);
+    const size_t partial = sp.splits > 1 ? (size_t)tiles * sp.splits * bt * 128 * sizeof(float) : 0;
+    return kTicketBytes + align_up(partial, 256);
+}
+
+int check_common(const void* x, const void* w, const void* scales, const void* out, int M, int N, int K, int block_h,
+                 int block_w, int scale_dtype) {
+    W8A16_REQUIRE(M >= 0 && N >= 0 && K >= 0, FP8W8A16_ERR_INVALID, "negative dimension M=%d N=%d K=%d", M, N, K);
+    if (M == 0 || N == 0) return 0;
+    W8A16_REQUIRE(x && w && scales && out, FP8W8A16_ERR_INVALID, "null pointer argument");
+    W8A16_REQUIRE(block_w == 128, FP8W8A16_ERR_UNSUPPORTED, "block_w must be 128 (got %d)", block_w);
+    W8A16_REQUIRE(block_h >= 1, FP8W8A16_ERR_INVALID, "block_h must be >= 1 (got %d)", block_h);
+    W8A16_REQUIRE(K > 0 && K % 16 == 0, FP8W8A16_ERR_UNSUPPORTED, "K must be a positive multiple of 16 (got %d)", K);
+    W8A16_REQUIRE(scale_dtype == FP8W8A16_SCALE_F16 || scale_dtype == FP8W8A16_SCALE_F32, FP8W8A16_ERR_INVALID,
+                  "unknown scale dtype %d", scale_dtype);
+    W8A16_REQUIRE(aligned16(x) && aligned16(w), FP8W8A16_ERR_INVALID, "x and w must be 16-byte aligned");
+    return 0;
+}
+
+int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_dtype, __half* out, int M, int N, int K,
+              int block_h, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    const int bt = tc_pick_bt(M), bk = tc_block_k(bt, false);
+    const int token_tiles = (M + bt - 1) / bt;
+    const int tiles = ((N + 127) / 128) * token_tiles;
+    const SplitPlan sp = plan_splits(tiles, tiles, K, bk);
+    TcLaunch L;
+    memset(&L, 0, sizeof(L));
+    L.p.M = M;
+    L.p.N = N;
+    L.p.K = K;
+    L.p.w_rows_per_expert = N;
+    L.p.pair_offset = 0;
+    L.p.scales = scales;
+    L.p.scale_dtype = scale_dtype;
+    L.p.block_h = block_h;
+    L.p.Kb = (K + 127) / 128;
+    L.p.scale_expert_stride = 0;
+    L.p.num_experts = 1;
+    L.p.out = out;
+    L.p.ldo = N;
+    L.p.splits = sp.splits;
+    L.p.kblocks_per_split = sp.kb_per_split;
+    if (sp.splits > 1) {
+        const size_t need = kTicketBytes + (size_t)tiles * sp.splits * bt * 128 * sizeof(float);
+        W8A16_REQUIRE(workspace != nullptr && workspace_bytes >= need, FP8W8A16_ERR_WORKSPACE,
+                      "linear: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
+        L.p.tickets = reinterpret_cast<unsigned int*>(workspace);
+        L.p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kTicketBytes);
+    }
+    L.w = w;
+    L.x = x;
+    L.w_total_rows = N;
+    L.token_tiles = token_tiles;
+    return tc_launch(L, bt, false, st);
+}
+
+int token_tile_for(int R, int E) {
+    const int avg = (R + E - 1) / E;
+    int bt = tc_pick_bt(2 * avg);
+    if (bt > 256) bt = 256;
+    return bt;
+}
+
+int token_tiles_upper_bound(int R, int E, int bt) { return (R < E ? R : E) + R / bt; }
+
+struct GroupedPlan {
+    int n_slabs, tiles_ub, bk;
+    SplitPlan sp;
+    size_t partial_bytes;
+};
+
+GroupedPlan plan_grouped(int R, int E, int N, int K, int paired, int bt) {
+    GroupedPlan g;
+    g.bk = tc_block_k(bt, paired != 0);
+    g.n_slabs = (N + 127) / 128;
+    g.tiles_ub = token_tiles_upper_bound(R, E, bt) * g.n_slabs;
+    const int active = (R < E ? R : E) * g.n_slabs;  // tiles that certainly stream distinct weights
+    g.sp = plan_splits(active > 0 ? active : 1, g.tiles_ub, K, g.bk);
+    g.partial_bytes = g.sp.splits > 1 ? (size_t)g.tiles_ub * g.sp.splits * (paired ? 2 : 1) * bt * 128 * sizeof(float) : 0;
+    return g;
+}
+
+int grouped_gemm(const __half* x_sorted, const uint8_t* w, const void* scales, int scale_dtype, __half* out,
+                 const float* row_weight, const int* offsets, const int* tile_offsets, int R, int E, int N, int K,
+                 int block_h, int paired, int bt, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    if (R == 0 || N == 0) return 0;
+    const GroupedPlan g = plan_grouped(R, E, N, K, paired, bt);
+    const int rows_w = paired ? 2 * N : N;
+    TcLaunch L;
+    memset(&L, 0, sizeof(L));
+    L.p.M = R;
+    L.p.N = N;
+    L.p.K = K;
+    L.p.w_rows_per_expert = rows_w;
+    L.p.pair_offset = paired ? N : 0;
+    L.p.scales = scales;
+    L.p.scale_dtype = scale_dtype;
+    L.p.block_h = block_h;
+    L.p.Kb = (K + 127) / 128;
+    L.p.scale_expert_stride = (int64_t)((rows_w + block_h - 1) / block_h) * L.p.Kb;
+    L.p.expert_offsets = offsets;
+    L.p.tile_offsets = tile_offsets;
+    L.p.num_experts = E;
+    L.p.out = out;
+    L.p.ldo = N;
+    L.p.row_weight = row_weight;
+    L.p.splits = g.sp.splits;
+    L.p.kblocks_per_split = g.sp.kb_per_split;
+    if (g.sp.splits > 1) {
+        const size_t need = kTicketBytes + g.partial_bytes;
+        W8A16_REQUIRE(workspace != nullptr && workspace_bytes >= need, FP8W8A16_ERR_WORKSPACE,
+                      "moe_grouped_gemm: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
+        L.p.tickets = reinterpret_cast<unsigned int*>(workspace);
+        L.p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kTicketBytes);
+    }
+    L.w = w;
+    L.x = x_sorted;
+    L.w_total_rows = (int64_t)E * rows_w;
+    L.token_tiles = token_tiles_upper_bound(R, E, bt);
+    return tc_launch(L, bt, paired != 0, st);
+}
+
+// Workspace of the whole MoE layer.
+struct MoeLayout {
+    size_t counts, offsets, tile_offsets, sorted_route, inv_pos, w_sorted, x_sorted, h_sorted, y_sorted, gemm_ws, total;
+    size_t gemm_ws_bytes;
+    int bt;
+};
+
+MoeLayout moe_layout(int M, int topk, int E, int H, int I) {
+    MoeLayout L;
+    const int R = M * topk;
+    L.bt = token_tile_for(R > 0 ? R : 1, E);
+    size_t o = kTicketBytes;  // the grouped GEMMs' ticket header sits at the very start
+    // the GEMM scratch (tickets + partials) must be one contiguous block: header first, partials
+    // right after it; the bookkeeping arrays follow the partials.
+    const GroupedPlan g13 = plan_grouped(R > 0 ? R : 1, E, I, H, 1, L.bt);
+    const GroupedPlan g2 = plan_grouped(R > 0 ? R : 1, E, H, I, 0, L.bt);
+    const size_t partial = g13.partial_bytes > g2.partial_bytes ? g13.partial_bytes : g2.partial_bytes;
+    L.gemm_ws = 0;
+    L.gemm_ws_bytes = kTicketBytes + align_up(partial, 256);
+    o = L.gemm_ws_bytes;
+    auto take = [&o](size_t bytes) {
+        const size_t at = o;
+        o += align_up(bytes, 256);
+        return at;
+    };
+    L.counts = take((size_t)E * 4);
+    L.offsets = take((size_t)(E + 1) * 4);
+    L.tile_offsets = take((size_t)(E + 1) * 4);
+    L.sorted_route = take((size_t)R * 4);
+    L.inv_pos = take((size_t)R * 4);
+    L.w_sorted = take((size_t)R * 4);
+    L.x_sorted = take((size_t)R * H * 2);
+    L.h_sorted = take((size_t)R * I * 2);
+    L.y_sorted = take((size_t)R * H * 2);
+    L.total = o;
+    return L;
+}
+
+}  // namespace
+}  // namespace w8a16
+
+using namespace w8a16;
+
+extern "C" {
+
+int fp8w8a16_version(void) { return 100; }
+
+const char* fp8w8a16_last_error(void) { return t_err; }
+
+int fp8w8a16_device_status(int* status, int reset) {
+    W8A16_REQUIRE(status != nullptr, FP8W8A16_ERR_INVALID, "device_status: null status pointer");
+    W8A16_CUDA(cudaDeviceSynchronize());
+    return tc_read_status(status, reset);
+}
+
+int fp8w8a16_e4m3_to_fp16(const uint8_t* w, uint16_t* out, int64_t n, void* stream) {
+    W8A16_REQUIRE(n >= 0, FP8W8A16_ERR_INVALID, "e4m3_to_fp16: negative n");
+    W8A16_REQUIRE(n == 0 || (w && out), FP8W8A16_ERR_INVALID, "e4m3_to_fp16: null pointer");
+    return launch_e4m3_to_fp16(w, reinterpret_cast<__half*>(out), n, (cudaStream_t)stream);
+}
+
+int fp8w8a16_e4m3_to_fp16_scaled(const uint8_t* w, const uint16_t* scales_f16, uint16_t* out, int64_t n,
+                                 int64_t group_size, void* stream) {
+    W8A16_REQUIRE(n >= 0 && group_size > 0, FP8W8A16_ERR_INVALID, "e4m3_to_fp16_scaled: n=%lld group=%lld", (long long)n,
+                  (long long)group_size);
+    W8A16_REQUIRE(n == 0 || (w && out && scales_f16), FP8W8A16_ERR_INVALID, "e4m3_to_fp16_scaled: null pointer");
+    return launch_e4m3_to_fp16_scaled(w, reinterpret_cast<const __half*>(scales_f16), reinterpret_cast<__half*>(out), n,
+                                      group_size, (cudaStream_t)stream);
+}
+
+int fp8w8a16_dequant_block_scaled(const uint8_t* w, const void* scales, int scale_dtype, uint16_t* out, int N, int K,
+                                  int block_h, int block_w, void* stream) {
+    W8A16_REQUIRE(N >= 0 && K >= 0, FP8W8A16_ERR_INVALID, "dequant_block_scaled: negative dimension");
+    W8A16_REQUIRE(block_h >= 1 && block_w >= 1, FP8W8A16_ERR_INVALID, "dequant_block_scaled: block %dx%d", block_h, block_w);
+    W8A16_REQUIRE(scale_dtype == FP8W8A16_SCALE_F16 || scale_dtype == FP8W8A16_SCALE_F32, FP8W8A16_ERR_INVALID,
+                  "dequant_block_scaled: unknown scale dtype %d", scale_dtype);
+    W8A16_REQUIRE((N == 0 || K == 0) || (w && scales && out), FP8W8A16_ERR_INVALID, "dequant_block_scaled: null pointer");
+    return launch_dequant_block(w, scales, scale_dtype, reinterpret_cast<__half*>(out), N, K, block_h, block_w,
+                                (cudaStream_t)stream);
+}
+
+size_t fp8w8a16_linear_workspace_bytes(int M, int N, int K) {
+    if (M <= 0 || N <= 0 || K <= 0) return kTicketBytes;
+    const size_t a = gemv_workspace_bytes(M, N, K);
+    const size_t b = tc_dense_workspace_bytes(M, N, K);
+    return a > b ? a : b;
+}
+
+int fp8w8a16_linear(const uint16_t* x, const uint8_t* w, const void* scales, int scale_dtype, uint16_t* out, int M,
+                    int N, int K, int block_h, int block_w, int algo, void* workspace, size_t workspace_bytes,
+                    void* stream) {
+    int rc = check_common(x, w, scales, out, M, N, K, block_h, block_w, scale_dtype);
+    if (rc) return rc;
+    if (M == 0 || N == 0) return 0;
+    const __half* xh = reinterpret_cast<const __half*>(x);
+    __half* oh = reinterpret_cast<__half*>(out);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (algo == FP8W8A16_ALGO_AUTO) algo = (M <= 4) ? FP8W8A16_ALGO_GEMV : FP8W8A16_ALGO_TC;
+    switch (algo) {
+        case FP8W8A16_ALGO_GEMV:
+            return launch_gemv(xh, w, scales, scale_dtype, oh, M, N, K, block_h, block_w, workspace, workspace_bytes, st);
+        case FP8W8A16_ALGO_TC:
+            return linear_tc(xh, w, scales, scale_dtype, oh, M, N, K, block_h, workspace, workspace_bytes, st);
+    }
+    return fail(FP8W8A16_ERR_INVALID, "linear: unknown algo %d", algo);
+}
+
+int fp8w8a16_moe_topk_softmax(const void* logits, int logits_dtype, int M, int E, int topk, int renormalize,
+                              int32_t* topk_ids, float* topk_weights, void* stream) {
+    W8A16_REQUIRE(M >= 0, FP8W8A16_ERR_INVALID, "moe_topk_softmax: negative M");
+    W8A16_REQUIRE(M == 0 || (logits && topk_ids && topk_weights), FP8W8A16_ERR_INVALID, "moe_topk_softmax: null pointer");
+    return launch_topk_softmax(logits, logits_dtype, M, E, topk, renormalize, topk_ids, topk_weights, (cudaStream_t)stream);
+}
+
+int fp8w8a16_moe_token_tile(int R, int num_local_experts) {
+    if (R <= 0 || num_local_experts <= 0) return 16;
+    return token_tile_for(R, num_local_experts);
+}
+
+int fp8w8a16_moe_align(const void* topk_ids, int ids_are_i64, int R, const int32_t* expert_map, int n_global_experts,
+                       int num_local_experts, int token_tile, int32_t* counts, int32_t* offsets, int32_t* tile_offsets,
+                       int32_t* sorted_route, int32_t* inv_pos, void* stream) {
+    W8A16_REQUIRE(R >= 0, FP8W8A16_ERR_INVALID, "moe_align: negative R");
+    W8A16_REQUIRE(token_tile >= 1, FP8W8A16_ERR_INVALID, "moe_align: token_tile=%d", token_tile);
+    W8A16_REQUIRE(counts && offsets && tile_offsets, FP8W8A16_ERR_INVALID, "moe_align: null output pointer");
+    W8A16_REQUIRE(R == 0 || (topk_ids && sorted_route && inv_pos), FP8W8A16_ERR_INVALID, "moe_align: null pointer");
+    return launch_align(topk_ids, ids_are_i64, R, expert_map, n_global_experts, num_local_experts, token_tile, counts, offsets,
+                        tile_offsets, sorted_route, inv_pos, (cudaStream_t)stream);
+}
+
+size_t fp8w8a16_moe_grouped_gemm_workspace_bytes(int R, int num_local_experts, int N, int K, int paired, int token_tile) {
+    if (R <= 0 || num_local_experts <= 0 || N <= 0 || K <= 0) return kTicketBytes;
+    const GroupedPlan g = plan_grouped(R, num_local_experts, N, K, paired, token_tile);
+    return kTicketBytes + align_up(g.partial_bytes, 256);
+}
+
+int fp8w8a16_moe_grouped_gemm(const uint16_t* x_sorted, const uint8_t* w, const void* scales, int scale_dtype,
+                              uint16_t* out, const float* row_weight, const int32_t* offsets,
+                              const int32_t* tile_offsets, int R, int num_local_experts, int N, int K, int block_h,
+                              int paired, int token_tile, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = check_common(x_sorted, w, scales, out, R, N, K, block_h, 128, scale_dtype);
+    if (rc) return rc;
+    W8A16_REQUIRE(num_local_experts >= 1, FP8W8A16_ERR_INVALID, "moe_grouped_gemm: num_local_experts=%d", num_local_experts);
+    W8A16_REQUIRE(token_tile == 16 || token_tile == 32 || token_tile == 64 || token_tile == 128 || token_tile == 256,
+                  FP8W8A16_ERR_INVALID, "moe_grouped_gemm: token_tile=%d not in {16,32,64,128,256}", token_tile);
+    W8A16_REQUIRE(R == 0 || (offsets && tile_offsets), FP8W8A16_ERR_INVALID, "moe_grouped_gemm: null route table");
+    return grouped_gemm(reinterpret_cast<const __half*>(x_sorted), w, scales, scale_dtype, reinterpret_cast<__half*>(out),
+                        row_weight, offsets, tile_offsets, R, num_local_experts, N, K, block_h, paired, token_tile, workspace,
+                        workspace_bytes, (cudaStream_t)stream);
+}
+
+int fp8w8a16_moe_gather(const uint16_t* x, const int32_t* sorted_route, const float* topk_weights, int R, int topk,
+                        int H, int weight_on_input, uint16_t* x_sorted, float* w_sorted, void* stream) {
+    W8A16_REQUIRE(R >= 0 && topk >= 1 && H >= 0, FP8W8A16_ERR_INVALID, "moe_gather: R=%d topk=%d H=%d", R, topk, H);
+    W8A16_REQUIRE(R == 0 || (x && sorted_route && topk_weights && x_sorted && w_sorted), FP8W8A16_ERR_INVALID,
+                  "moe_gather: null pointer");
+    return launch_gather(reinterpret_cast<const __half*>(x), sorted_route, topk_weights, R, topk, H, weight_on_input,
+                         reinterpret_cast<__half*>(x_sorted), w_sorted, (cudaStream_t)stream);
+}
+
+int fp8w8a16_moe_combine(const uint16_t* y_sorted, const int32_t* inv_pos, int M, int topk, int H, uint16_t* out,
+                         void* stream) {
+    W8A16_REQUIRE(M >= 0 && topk >= 1 && H >= 0, FP8W8A16_ERR_INVALID, "moe_combine: M=%d topk=%d H=%d", M, topk, H);
+    W8A16_REQUIRE(M == 0 || (y_sorted && inv_pos && out), FP8W8A16_ERR_INVALID, "moe_combine: null pointer");
+    return launch_combine(reinterpret_cast<const __half*>(y_sorted), inv_pos, M, topk, H, reinterpret_cast<__half*>(out),
+                          (cudaStream_t)stream);
+}
+
+size_t fp8w8a16_moe_workspace_bytes(int M, int topk, int num_local_experts, int H, int I) {
+    if (M <= 0 || topk <= 0 || num_local_experts <= 0 || H <= 0 || I <= 0) return kTicketBytes;
+    return moe_layout(M, topk, num_local_experts, H, I).total;
+}
+
+int fp8w8a16_moe_forward(const uint16_t* x, const void* topk_ids, int ids_are_i64, const float* topk_weights,
+                         const int32_t* expert_map, int n_global_experts, const uint8_t* w13, const void* s13,
+                         const uint8_t* w2, const void* s2, int scale_dtype, uint16_t* out, int M, int topk,
+                         int num_local_experts, int H, int I, int block_h, int weight_on_input, void* workspace,
+                         size_t workspace_bytes, void* stream) {
+    W8A16_REQUIRE(M >= 0 && topk >= 1 && num_local_experts >= 1 && H > 0 && I > 0, FP8W8A16_ERR_INVALID,
+                  "moe_forward: M=%d topk=%d E=%d H=%d I=%d", M, topk, num_local_experts, H, I);
+    if (M == 0) return 0;
+    W8A16_REQUIRE(x && topk_ids && topk_weights && w13 && s13 && w2 && s2 && out, FP8W8A16_ERR_INVALID,
+                  "moe_forward: null pointer");
+    W8A16_REQUIRE(H % 16 == 0 && I % 16 == 0, FP8W8A16_ERR_UNSUPPORTED,
+                  "moe_forward: hidden %d and intermediate %d must be multiples of 16", H, I);
+    W8A16_REQUIRE(block_h >= 1, FP8W8A16_ERR_INVALID, "moe_forward: block_h=%d", block_h);
+    W8A16_REQUIRE((int64_t)M * topk < (1ll << 30), FP8W8A16_ERR_UNSUPPORTED, "moe_forward: too many routed rows");
+    const int E = num_local_experts, R = M * topk;
+    const MoeLayout L = moe_layout(M, topk, E, H, I);
+    W8A16_REQUIRE(workspace != nullptr && workspace_bytes >= L.total, FP8W8A16_ERR_WORKSPACE,
+                  "moe_forward: workspace too small (%zu < %zu bytes)", workspace_bytes, L.total);
+    W8A16_REQUIRE(aligned16(workspace) && aligned16(x) && aligned16(out), FP8W8A16_ERR_INVALID,
+                  "moe_forward: x, out and workspace must be 16-byte aligned");
+    char* ws = reinterpret_cast<char*>(workspace);
+    int* counts = reinterpret_cast<int*>(ws + L.counts);
+    int* offsets = reinterpret_cast<int*>(ws + L.offsets);
+    int* tile_offsets = reinterpret_cast<int*>(ws + L.tile_offsets);
+    int* sorted_route = reinterpret_cast<int*>(ws + L.sorted_route);
+    int* inv_pos = reinterpret_cast<int*>(ws + L.inv_pos);
+    float* w_sorted = reinterpret_cast<float*>(ws + L.w_sorted);
+    __half* x_sorted = reinterpret_cast<__half*>(ws + L.x_sorted);
+    __half* h_sorted = reinterpret_cast<__half*>(ws + L.h_sorted);
+    __half* y_sorted = reinterpret_cast<__half*>(ws + L.y_sorted);
+    cudaStream_t st = (cudaStream_t)stream;
+
+    int rc = launch_align(topk_ids, ids_are_i64, R, expert_map, n_global_experts, E, L.bt, counts, offsets, tile_offsets,
+                          sorted_route, inv_pos, st);
+    if (rc) return rc;
+    rc = launch_gather(reinterpret_cast<const __half*>(x), sorted_route, topk_weights, R, topk, H, weight_on_input, x_sorted,
+                       w_sorted, st);
+    if (rc) return rc;
+    rc = grouped_gemm(x_sorted, w13, s13, scale_dtype, h_sorted, nullptr, offsets, tile_offsets, R, E, I, H, block_h, 1, L.bt,
+                      ws + L.gemm_ws, L.gemm_ws_bytes, st);
+    if (rc) return rc;
+    rc = grouped_gemm(h_sorted, w2, s2, scale_dtype, y_sorted, w_sorted, offsets, tile_offsets, R, E, H, I, block_h, 0, L.bt,
+                      ws + L.gemm_ws, L.gemm_ws_bytes, st);
+    if (rc) return rc;
+    return launch_combine(y_sorted, inv_pos, M, topk, H, reinterpret_cast<__half*>(out), st);
+}
+
+}  // extern "C"

@@ -1,0 +1,51 @@
+// Launch parameters of the tcgen05 W8A16 GEMM (see gemm_tc.cu).
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace w8a16 {
+
+struct TcParams {
+    int M;                       // rows of the activation matrix (dense: tokens; grouped: all sorted rows)
+    int N;                       // output features (paired gate/up mode: the intermediate size I)
+    int K;
+    // weights: [num_experts * w_rows_per_expert, K] E4M3 bytes, row-major
+    int w_rows_per_expert;       // N, or 2 * I in paired mode
+    int pair_offset;             // I in paired mode (up rows follow gate rows), else 0
+    // scale grid per expert: [ceil(rows / block_h), Kb], fp16 or fp32
+    const void* scales;
+    int scale_dtype;
+    int block_h;
+    int Kb;
+    int64_t scale_expert_stride; // elements between experts in the scale grid
+    // grouped mode (null pointers = dense)
+    const int* expert_offsets;   // [E + 1] first sorted row of each expert
+    const int* tile_offsets;     // [E + 1] first token tile of each expert (prefix sum of ceil(count / BT))
+    int num_experts;
+    // output
+    __half* out;                 // out[row * ldo + n]
+    int64_t ldo;
+    const float* row_weight;     // optional per-row multiplier (route weight), applied as FP16
+    // split-K
+    float* partial;              // fp32 scratch: [tiles][splits][(1|2)][BT][128]
+    unsigned int* tickets;       // one counter per tile, zero on entry and on exit
+    int splits;
+    int kblocks_per_split;
+};
+
+struct TcLaunch {
+    TcParams p;
+    const uint8_t* w;
+    const __half* x;
+    int64_t w_total_rows;        // num_experts * w_rows_per_expert
+    int token_tiles;             // gridDim.y (dense: ceil(M / BT); grouped: an upper bound)
+};
+
+int tc_pick_bt(int rows);
+int tc_block_k(int bt, bool paired);
+int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st);
+int tc_read_status(int* out, int reset);
+
+}  // namespace w8a16

@@ -1,0 +1,224 @@
+// Decode GEMV for 1..4 tokens: C[m,n] = sum_k A[m,k] * cvt(W[n,k]) * S[n/bh, k/128]
+//
+// HBM-bound on the FP8 weight stream.  One warp owns R = 4 consecutive weight rows and one K range;
+// a lane reads 16 weight bytes per row per step (a warp covers 512 contiguous bytes of each row with
+// one 16-byte load per lane), so 4 independent 16-byte loads per lane are in flight per step and the
+// activations are fetched once per step for all 4 rows.  Dequant happens in registers, products are
+// accumulated in fp32 per 16-element run and multiplied by the block (or channel) scale once per
+// run, the lanes are reduced with warp shuffles.  K is split across blockIdx.y; partial sums go to
+// an fp32 workspace and the LAST CTA to arrive for a row block (ticket counter) adds them in fixed
+// split order, so the result does not depend on scheduling.
+//
+// Replaces the reference's decode kernels fp8_w8a16_gemv_coalesced / _coalesced_m / gemm_a3
+// (src/fp8_w8a16_sm70/fp8_dequant.cu:622-786, 535-594).
+#include "common.cuh"
+
+namespace w8a16 {
+
+namespace {
+
+constexpr int kRows = 4;               // weight rows per warp
+constexpr int kWarps = 8;              // warps per CTA
+constexpr int kThreads = kWarps * 32;
+constexpr int kRowsPerCta = kRows * kWarps;
+constexpr int kStep = 512;             // K elements one warp covers per step
+
+// 16 E4M3 bytes (uint4) times 16 activations -> fp32 dot product, weights taken as
+// (magnitude * 2^-8) with sign; the caller folds 2^8 into the scale.
+template <int M>
+__device__ __forceinline__ void dot16(const uint4& q, const float (&xf)[M][16], float (&part)[M]) {
+    const uint32_t words[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        uint32_t m01, g01, m23, g23;
+        e4m3x2_split(words[t], 0x1404u, m01, g01);
+        e4m3x2_split(words[t], 0x3424u, m23, g23);
+        m01 ^= g01;
+        m23 ^= g23;
+        const float2 w01 = __half22float2(*reinterpret_cast<__half2*>(&m01));
+        const float2 w23 = __half22float2(*reinterpret_cast<__half2*>(&m23));
+#pragma unroll
+        for (int m = 0; m < M; ++m) {
+            part[m] = fmaf(w01.x, xf[m][4 * t + 0], part[m]);
+            part[m] = fmaf(w01.y, xf[m][4 * t + 1], part[m]);
+            part[m] = fmaf(w23.x, xf[m][4 * t + 2], part[m]);
+            part[m] = fmaf(w23.y, xf[m][4 * t + 3], part[m]);
+        }
+    }
+}
+
+template <int M>
+__global__ void __launch_bounds__(kThreads)
+k_gemv(const __half* __restrict__ x, const uint8_t* __restrict__ w, const void* __restrict__ scales, int scale_dtype,
+       __half* __restrict__ out, float* __restrict__ partial, unsigned int* __restrict__ tickets, int N, int K,
+       int block_h, int Kb, int k_chunk, int splits) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row0 = blockIdx.x * kRowsPerCta + warp * kRows;
+    const int split = blockIdx.y;
+    const int k_begin = split * k_chunk;
+    const int k_end = min(K, k_begin + k_chunk);
+
+    float acc[kRows][M];
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = 0.f;
+
+    if (row0 < N) {
+        const uint8_t* wrow[kRows];
+        int srow[kRows];
+#pragma unroll
+        for (int r = 0; r < kRows; ++r) {
+            const int n = min(row0 + r, N - 1);  // clamp: out-of-range rows are computed and dropped
+            wrow[r] = w + (int64_t)n * K;
+            srow[r] = (n / block_h) * Kb;
+        }
+        const bool one_scale = (block_h % kRows) == 0;  // all 4 rows share the scale-grid row
+
+        for (int k = k_begin + lane * 16; k < k_end; k += kStep) {
+            uint4 q[kRows];
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) q[r] = __ldcs(reinterpret_cast<const uint4*>(wrow[r] + k));
+            float xf[M][16];
+#pragma unroll
+            for (int m = 0; m < M; ++m) {
+                const uint4 a0 = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)m * K + k));
+                const uint4 a1 = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)m * K + k) + 1);
+                const uint32_t aw[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
+                    xf[m][2 * i] = f.x;
+                    xf[m][2 * i + 1] = f.y;
+                }
+            }
+            const int kb = k >> 7;
+            float s[kRows];
+            if (one_scale) {
+                const float s0 = __half2float(load_scale_h(scales, srow[0] + kb, scale_dtype)) * 256.f;
+#pragma unroll
+                for (int r = 0; r < kRows; ++r) s[r] = s0;
+            } else {
+#pragma unroll
+                for (int r = 0; r < kRows; ++r)
+                    s[r] = __half2float(load_scale_h(scales, srow[r] + kb, scale_dtype)) * 256.f;
+            }
+#pragma unroll
+            for (int r = 0; r < kRows; ++r) {
+                float part[M];
+#pragma unroll
+                for (int m = 0; m < M; ++m) part[m] = 0.f;
+                dot16<M>(q[r], xf, part);
+#pragma unroll
+                for (int m = 0; m < M; ++m) acc[r][m] = fmaf(s[r], part[m], acc[r][m]);
+            }
+        }
+    }
+
+#pragma unroll
+    for (int r = 0; r < kRows; ++r)
+#pragma unroll
+        for (int m = 0; m < M; ++m) acc[r][m] = warp_sum(acc[r][m]);
+
+    if (splits == 1) {
+        if (lane == 0) {
+#pragma unroll
+            for (int r = 0; r < kRows; ++r)
+                if (row0 + r < N)
+#pragma unroll
+                    for (int m = 0; m < M; ++m) out[(int64_t)m * N + row0 + r] = __float2half_rn(acc[r][m]);
+        }
+        return;
+    }
+
+    // split-K: publish this CTA's partial sums, then the last CTA of the row block reduces them.
+    if (lane == 0) {
+#pragma unroll
+        for (int r = 0; r < kRows; ++r)
+            if (row0 + r < N)
+#pragma unroll
+                for (int m = 0; m < M; ++m) __stcg(&partial[((int64_t)split * M + m) * N + row0 + r], acc[r][m]);
+    }
+    __threadfence();
+    __syncthreads();
+    __shared__ unsigned int s_ticket;
+    if (threadIdx.x == 0) s_ticket = atomicAdd(&tickets[blockIdx.x], 1u);
+    __syncthreads();
+    if (s_ticket != (unsigned)(splits - 1)) return;
+    __threadfence();
+    const int base = blockIdx.x * kRowsPerCta;
+    for (int i = threadIdx.x; i < kRowsPerCta * M; i += kThreads) {
+        const int m = i / kRowsPerCta, n = base + (i - m * kRowsPerCta);
+        if (n < N) {
+            float v = 0.f;
+            for (int sp = 0; sp < splits; ++sp) v += __ldcg(&partial[((int64_t)sp * M + m) * N + n]);
+            out[(int64_t)m * N + n] = __float2half_rn(v);
+        }
+    }
+    if (threadIdx.x == 0) tickets[blockIdx.x] = 0u;  // self-cleaning for the next launch
+}
+
+}  // namespace
+
+// Number of K splits for a GEMV over [N,K]: enough warps to keep every SM's load queue full, but
+// at least two 512-element steps per warp.
+int gemv_pick_splits(int N, int K) {
+    const int row_blocks = (N + kRowsPerCta - 1) / kRowsPerCta;
+    const int want_ctas = sm_count() * 6;
+    int s = (want_ctas + row_blocks - 1) / row_blocks;
+    const int max_s = (K / (2 * kStep)) > 0 ? K / (2 * kStep) : 1;
+    if (s > max_s) s = max_s;
+    if (s > 32) s = 32;
+    if (s < 1) s = 1;
+    return s;
+}
+
+size_t gemv_workspace_bytes(int M, int N, int K) {
+    const int splits = gemv_pick_splits(N, K);
+    const int mm = M < 4 ? M : 4;
+    const size_t partial = splits > 1 ? (size_t)splits * mm * N * sizeof(float) : 0;
+    return kTicketBytes + ((partial + 255) & ~(size_t)255);
+}
+
+// Workspace layout: ticket counters in the first kTicketBytes (zero on entry, left at zero on
+// exit), fp32 partial sums after them (no initialisation needed).
+int launch_gemv(const __half* x, const uint8_t* w, const void* scales, int scale_dtype, __half* out, int M, int N,
+                int K, int block_h, int block_w, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+    W8A16_REQUIRE(block_w == 128, FP8W8A16_ERR_UNSUPPORTED, "gemv: block_w must be 128 (got %d)", block_w);
+    W8A16_REQUIRE(K % 16 == 0, FP8W8A16_ERR_UNSUPPORTED, "gemv: K must be a multiple of 16 (got %d)", K);
+    W8A16_REQUIRE(aligned16(x) && aligned16(w), FP8W8A16_ERR_INVALID, "gemv: x and w must be 16-byte aligned");
+    if (M == 0 || N == 0) return 0;
+    const int Kb = (K + 127) / 128;
+    const int row_blocks = (N + kRowsPerCta - 1) / kRowsPerCta;
+    int splits = gemv_pick_splits(N, K);
+    int k_chunk = ((K + splits - 1) / splits + kStep - 1) / kStep * kStep;
+    splits = (K + k_chunk - 1) / k_chunk;
+    float* partial = nullptr;
+    unsigned int* tickets = nullptr;
+    if (splits > 1) {
+        const size_t need = gemv_workspace_bytes(M, N, K);
+        W8A16_REQUIRE(workspace != nullptr && workspace_bytes >= need, FP8W8A16_ERR_WORKSPACE,
+                      "gemv: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
+        W8A16_REQUIRE((size_t)row_blocks * sizeof(unsigned int) <= kTicketBytes, FP8W8A16_ERR_UNSUPPORTED,
+                      "gemv: N=%d needs more ticket counters than the workspace header holds", N);
+        tickets = reinterpret_cast<unsigned int*>(workspace);
+        partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kTicketBytes);
+    }
+    const dim3 grid(row_blocks, splits);
+    for (int m0 = 0; m0 < M; m0 += 4) {  // more than 4 tokens: the weight is streamed once per 4 tokens
+        const int mc = (M - m0) < 4 ? (M - m0) : 4;
+        const __half* xm = x + (int64_t)m0 * K;
+        __half* om = out + (int64_t)m0 * N;
+        switch (mc) {
+            case 1: k_gemv<1><<<grid, kThreads, 0, st>>>(xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits); break;
+            case 2: k_gemv<2><<<grid, kThreads, 0, st>>>(xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits); break;
+            case 3: k_gemv<3><<<grid, kThreads, 0, st>>>(xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits); break;
+            default: k_gemv<4><<<grid, kThreads, 0, st>>>(xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits); break;
+        }
+        int rc = check_launch("gemv");
+        if (rc) return rc;
+    }
+    return 0;
+}
+
+}  // namespace w8a16

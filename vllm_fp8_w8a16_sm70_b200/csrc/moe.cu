@@ -1,0 +1,325 @@
+// Device-side routing and bookkeeping kernels of the MoE layer.  Nothing here synchronises with
+// the host, so the whole layer can be captured in a CUDA graph.
+//
+//   topk_softmax : router logits -> top-k expert ids + weights (what vLLM's fused_topk hands to the
+//                  reference's MoE apply, src/fp8_w8a16_sm70/vllm_serve.py:2175).
+//   align        : expert_map remap (vllm_serve.py:2237-2243), per-expert counts, offsets, token-tile
+//                  table and a STABLE expert-sorted permutation of the routed rows (the reference's
+//                  sync-free route table: compressed_tensors_v100.py:776-784).
+//   gather       : activations -> expert-sorted rows (reference: index_select, vllm_serve.py:1862).
+//   combine      : weighted expert outputs -> one row per token (reference: index_add_, :1990).
+#include <cuda_bf16.h>
+
+#include "common.cuh"
+
+namespace w8a16 {
+
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// top-k softmax: one warp per token.  Selection is on the logits (ties -> lowest expert index);
+// the weights are the fp32 softmax probabilities of the selected experts, optionally renormalised.
+// ------------------------------------------------------------------------------------------------
+constexpr int kMaxPerLane = 32;  // experts <= 1024
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T, int PER_LANE>
+__global__ void __launch_bounds__(128) k_topk_softmax(const T* __restrict__ logits, int M, int E, int topk, int renorm,
+                                                      int* __restrict__ ids, float* __restrict__ weights) {
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= M) return;
+    const T* row = logits + (int64_t)warp * E;
+    float v[PER_LANE];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) {
+        const int e = i * 32 + lane;
+        v[i] = e < E ? to_f32<T>(row[e]) : -INFINITY;
+        mx = fmaxf(mx, v[i]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, o));
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < PER_LANE; ++i) sum += (i * 32 + lane < E) ? expf(v[i] - mx) : 0.f;
+    sum = warp_sum(sum);
+
+    uint32_t taken = 0;  // bit i: this lane's i-th expert already selected
+    float wsel = 0.f;    // lane t keeps the weight of the t-th pick
+    int isel = 0;
+    float wtot = 0.f;
+    for (int t = 0; t < topk; ++t) {
+        float best = -INFINITY;
+        int best_e = 0x7FFFFFFF;
+#pragma unroll
+        for (int i = 0; i < PER_LANE; ++i) {
+            const int e = i * 32 + lane;
+            if (e < E && !((taken >> i) & 1u) && (v[i] > best)) {  // ascending e inside a lane: strict > keeps the lowest index
+                best = v[i];
+                best_e = e;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xFFFFFFFFu, best, o);
+            const int oe = __shfl_xor_sync(0xFFFFFFFFu, best_e, o);
+            if (ob > best || (ob == best && oe < best_e)) {
+                best = ob;
+                best_e = oe;
+            }
+        }
+        if (best_e != 0x7FFFFFFF && (best_e & 31) == lane) taken |= 1u << (best_e >> 5);
+        const float pw = expf(best - mx) / sum;
+        wtot += pw;
+        if (lane == (t & 31)) {
+            wsel = pw;
+            isel = best_e;
+        }
+        if ((t & 31) == 31 || t == topk - 1) {  // flush up to 32 picks
+            const int t0 = t & ~31;
+            if (t0 + lane <= t) {
+                ids[(int64_t)warp * topk + t0 + lane] = isel;
+                weights[(int64_t)warp * topk + t0 + lane] = wsel;
+            }
+        }
+    }
+    if (renorm) {
+        __syncwarp();
+        for (int t = lane; t < topk; t += 32) weights[(int64_t)warp * topk + t] /= wtot;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// align: one CTA.  Stable counting sort of the routed rows by local expert id.
+// ------------------------------------------------------------------------------------------------
+constexpr int kAlignThreads = 1024;
+constexpr int kAlignWarps = kAlignThreads / 32;
+
+template <typename IdT>
+__device__ __forceinline__ int local_expert(const IdT* ids, int i, const int* expert_map, int n_global, int E) {
+    long long g = (long long)ids[i];
+    if (g < 0) return -1;
+    if (expert_map != nullptr) {
+        if (g >= n_global) return -1;
+        g = expert_map[g];
+    }
+    return (g >= 0 && g < E) ? (int)g : -1;
+}
+
+template <typename IdT>
+__global__ void __launch_bounds__(kAlignThreads)
+k_align(const IdT* __restrict__ ids, int R, const int* __restrict__ expert_map, int n_global, int E, int bt,
+        int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ tile_offsets,
+        int* __restrict__ sorted_route, int* __restrict__ inv_pos) {
+    extern __shared__ int sm[];
+    int* warp_hist = sm;                       // [kAlignWarps][E] -> later: running placement cursor
+    int* s_off = sm + kAlignWarps * E;         // [E + 1]
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    for (int i = tid; i < kAlignWarps * E; i += kAlignThreads) warp_hist[i] = 0;
+    __syncthreads();
+
+    // contiguous segment of routes per warp, walked in order 32 at a time
+    const int per_warp = ((R + kAlignWarps - 1) / kAlignWarps + 31) & ~31;
+    const int seg_begin = min(R, warp * per_warp), seg_end = min(R, seg_begin + per_warp);
+    for (int base = seg_begin; base < seg_end; base += 32) {
+        const int i = base + lane;
+        const int e = i < seg_end ? local_expert(ids, i, expert_map, n_global, E) : -1;
+        if (e >= 0) atomicAdd(&warp_hist[warp * E + e], 1);
+    }
+    __syncthreads();
+    // per expert: total count; turn per-warp counts into exclusive prefix over warps
+    for (int e = tid; e < E; e += kAlignThreads) {
+        int run = 0;
+        for (int w = 0; w < kAlignWarps; ++w) {
+            const int c = warp_hist[w * E + e];
+            warp_hist[w * E + e] = run;
+            run += c;
+        }
+        counts[e] = run;
+        s_off[e] = run;  // counts for now
+    }
+    __syncthreads();
+    if (tid == 0) {  // E is small (<= 1024): a serial scan is a few microseconds at most
+        int run = 0, trun = 0;
+        for (int e = 0; e < E; ++e) {
+            const int c = s_off[e];
+            s_off[e] = run;
+            offsets[e] = run;
+            tile_offsets[e] = trun;
+            run += c;
+            trun += (c + bt - 1) / bt;
+        }
+        s_off[E] = run;
+        offsets[E] = run;
+        tile_offsets[E] = trun;
+    }
+    __syncthreads();
+    const int n_valid = s_off[E];
+    for (int base = seg_begin; base < seg_end; base += 32) {
+        const int i = base + lane;
+        const int e = i < seg_end ? local_expert(ids, i, expert_map, n_global, E) : -1;
+        const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
+        if (e >= 0) {
+            const int rank = __popc(peers & ((1u << lane) - 1u));
+            const int cur = warp_hist[warp * E + e];
+            const int pos = s_off[e] + cur + rank;
+            sorted_route[pos] = i;
+            inv_pos[i] = pos;
+            __syncwarp(peers);
+            if (rank == 0) warp_hist[warp * E + e] = cur + __popc(peers);
+        } else if (i < seg_end) {
+            inv_pos[i] = -1;
+        }
+        __syncwarp();
+    }
+    for (int i = n_valid + tid; i < R; i += kAlignThreads) sorted_route[i] = -1;
+}
+
+// ------------------------------------------------------------------------------------------------
+// gather: x_sorted[pos] = x[route / topk] (optionally x route weight), w_sorted[pos] = weight[route].
+// One warp per sorted row, 16-byte copies.  Rows past the valid count are zero-filled so that the
+// token tiles of the grouped GEMM never read uninitialised memory.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_gather(const __half* __restrict__ x, const int* __restrict__ sorted_route, const float* __restrict__ topk_w, int R,
+         int topk, int H, int weight_on_input, __half* __restrict__ x_sorted, float* __restrict__ w_sorted) {
+    const int pos = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (pos >= R) return;
+    const int route = sorted_route[pos];
+    uint4* dst = reinterpret_cast<uint4*>(x_sorted + (int64_t)pos * H);
+    const int vecs = H >> 3;
+    if (route < 0) {
+        for (int i = lane; i < vecs; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
+        if (lane == 0) w_sorted[pos] = 0.f;
+        return;
+    }
+    const float wt = topk_w[route];
+    const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)(route / topk) * H);
+    if (!weight_on_input) {
+        for (int i = lane; i < vecs; i += 32) dst[i] = __ldg(src + i);
+        if (lane == 0) w_sorted[pos] = wt;
+    } else {
+        // reference: route_x * route_w.unsqueeze(-1) on FP16 tensors (vllm_serve.py:1868-1870)
+        const __half w16 = __float2half_rn(wt);
+        const __half2 w2 = __halves2half2(w16, w16);
+        for (int i = lane; i < vecs; i += 32) {
+            uint4 v = __ldg(src + i);
+            __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) h[j] = __hmul2(h[j], w2);
+            dst[i] = v;
+        }
+        if (lane == 0) w_sorted[pos] = 1.f;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// combine: out[token] = sum over the token's routes of y_sorted[inv_pos[route]] (already weighted),
+// summed in fp32 in route order, rounded once.  One CTA per token.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+k_combine(const __half* __restrict__ y_sorted, const int* __restrict__ inv_pos, int topk, int H, __half* __restrict__ out) {
+    const int token = blockIdx.x;
+    extern __shared__ int s_pos[];
+    for (int j = threadIdx.x; j < topk; j += blockDim.x) s_pos[j] = inv_pos[(int64_t)token * topk + j];
+    __syncthreads();
+    const int vecs = H >> 3;
+    for (int i = threadIdx.x; i < vecs; i += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) acc[c] = 0.f;
+        for (int j = 0; j < topk; ++j) {
+            const int pos = s_pos[j];
+            if (pos < 0) continue;
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(y_sorted + (int64_t)pos * H) + i);
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                const float2 f = __half22float2(h[c]);
+                acc[2 * c] += f.x;
+                acc[2 * c + 1] += f.y;
+            }
+        }
+        uint4 o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) oh[c] = __floats2half2_rn(acc[2 * c], acc[2 * c + 1]);
+        reinterpret_cast<uint4*>(out + (int64_t)token * H)[i] = o;
+    }
+}
+
+template <typename T>
+int launch_topk_t(const T* logits, int M, int E, int topk, int renorm, int* ids, float* weights, cudaStream_t st) {
+    const int per_lane = (E + 31) / 32;
+    const unsigned blocks = (unsigned)((M + 3) / 4);
+#define W8A16_TOPK(PL) k_topk_softmax<T, PL><<<blocks, 128, 0, st>>>(logits, M, E, topk, renorm, ids, weights)
+    if (per_lane <= 1) W8A16_TOPK(1);
+    else if (per_lane <= 2) W8A16_TOPK(2);
+    else if (per_lane <= 4) W8A16_TOPK(4);
+    else if (per_lane <= 8) W8A16_TOPK(8);
+    else if (per_lane <= 16) W8A16_TOPK(16);
+    else W8A16_TOPK(32);
+#undef W8A16_TOPK
+    return check_launch("moe_topk_softmax");
+}
+
+}  // namespace
+
+int launch_topk_softmax(const void* logits, int logits_dtype, int M, int E, int topk, int renorm, int* ids, float* weights,
+                        cudaStream_t st) {
+    W8A16_REQUIRE(E >= 1 && E <= 32 * kMaxPerLane, FP8W8A16_ERR_UNSUPPORTED, "topk_softmax: E=%d out of range [1,1024]", E);
+    W8A16_REQUIRE(topk >= 1 && topk <= E, FP8W8A16_ERR_INVALID, "topk_softmax: topk=%d must be in [1,E=%d]", topk, E);
+    if (M == 0) return 0;
+    switch (logits_dtype) {
+        case FP8W8A16_DTYPE_F32: return launch_topk_t(reinterpret_cast<const float*>(logits), M, E, topk, renorm, ids, weights, st);
+        case FP8W8A16_DTYPE_F16: return launch_topk_t(reinterpret_cast<const __half*>(logits), M, E, topk, renorm, ids, weights, st);
+        case FP8W8A16_DTYPE_BF16: return launch_topk_t(reinterpret_cast<const __nv_bfloat16*>(logits), M, E, topk, renorm, ids, weights, st);
+    }
+    return fail(FP8W8A16_ERR_INVALID, "topk_softmax: unknown logits dtype %d", logits_dtype);
+}
+
+int launch_align(const void* ids, int ids_are_i64, int R, const int* expert_map, int n_global, int E, int bt, int* counts,
+                 int* offsets, int* tile_offsets, int* sorted_route, int* inv_pos, cudaStream_t st) {
+    W8A16_REQUIRE(E >= 1 && E <= 1024, FP8W8A16_ERR_UNSUPPORTED, "moe_align: E=%d out of range [1,1024]", E);
+    const size_t smem = ((size_t)kAlignWarps * E + E + 1) * sizeof(int);
+    if (ids_are_i64) {
+        static bool set64 = false;
+        if (!set64 && smem > 48 * 1024) {
+            W8A16_CUDA(cudaFuncSetAttribute(k_align<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            set64 = true;
+        }
+        k_align<long long><<<1, kAlignThreads, smem, st>>>(reinterpret_cast<const long long*>(ids), R, expert_map, n_global, E, bt,
+                                                            counts, offsets, tile_offsets, sorted_route, inv_pos);
+    } else {
+        static bool set32 = false;
+        if (!set32 && smem > 48 * 1024) {
+            W8A16_CUDA(cudaFuncSetAttribute(k_align<int>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+            set32 = true;
+        }
+        k_align<int><<<1, kAlignThreads, smem, st>>>(reinterpret_cast<const int*>(ids), R, expert_map, n_global, E, bt, counts,
+                                                      offsets, tile_offsets, sorted_route, inv_pos);
+    }
+    return check_launch("moe_align");
+}
+
+int launch_gather(const __half* x, const int* sorted_route, const float* topk_w, int R, int topk, int H, int weight_on_input,
+                  __half* x_sorted, float* w_sorted, cudaStream_t st) {
+    W8A16_REQUIRE(H % 8 == 0, FP8W8A16_ERR_UNSUPPORTED, "moe_gather: hidden size %d must be a multiple of 8", H);
+    if (R == 0) return 0;
+    k_gather<<<(unsigned)((R + 7) / 8), 256, 0, st>>>(x, sorted_route, topk_w, R, topk, H, weight_on_input, x_sorted, w_sorted);
+    return check_launch("moe_gather");
+}
+
+int launch_combine(const __half* y_sorted, const int* inv_pos, int M, int topk, int H, __half* out, cudaStream_t st) {
+    W8A16_REQUIRE(H % 8 == 0, FP8W8A16_ERR_UNSUPPORTED, "moe_combine: hidden size %d must be a multiple of 8", H);
+    if (M == 0) return 0;
+    k_combine<<<(unsigned)M, 256, topk * sizeof(int), st>>>(y_sorted, inv_pos, topk, H, out);
+    return check_launch("moe_combine");
+}
+
+}  // namespace w8a16

@@ -1,0 +1,318 @@
+"""torch-tensor front end of the C ABI: the op surface the reference exposes through pybind
+(``src/fp8_w8a16_sm70/fp8_dequant.cu:3218-3298``), on one B200 engine.
+
+PyTorch is plumbing here: tensors carry device memory, ``torch.cuda.current_stream`` names the
+stream every kernel is launched on (the reference's stream rule, ``fp8_dequant.cu:29-36``).  All
+compute happens in the CUDA library; a missing library or a CPU tensor raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _cabi
+from ._cabi import ALGO_AUTO, ALGO_GEMV, ALGO_TC, SCALE_F16, SCALE_F32  # noqa: F401
+
+_WORKSPACES: dict = {}
+_TICKET_BYTES = 65536
+
+
+def _stream(dev: torch.device) -> int:
+    return torch.cuda.current_stream(dev).cuda_stream
+
+
+def _require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("fp8_w8a16 ops run on CUDA tensors only (no CPU fallback)")
+        if t.device != dev:
+            raise RuntimeError("all tensors must be on the same device")
+        if not t.is_contiguous():
+            raise RuntimeError("tensors must be contiguous")
+    return dev
+
+
+def _as_u8(w: torch.Tensor) -> torch.Tensor:
+    if w.dtype == torch.uint8:
+        return w
+    if w.dtype == torch.float8_e4m3fn:
+        return w.view(torch.uint8)
+    raise RuntimeError(f"weight must be uint8 or float8_e4m3fn (got {w.dtype})")
+
+
+def _scale_dtype(s: torch.Tensor) -> int:
+    if s.dtype == torch.float16:
+        return SCALE_F16
+    if s.dtype == torch.float32:
+        return SCALE_F32
+    raise RuntimeError(f"scales must be float16 or float32 (got {s.dtype}); cast bf16 scales at load")
+
+
+def workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
+    """Per (device, stream) scratch buffer.  The first 64 KiB hold the kernels' hand-off counters:
+    zero when allocated, left at zero by every kernel.  Grows on demand (a new zeroed buffer)."""
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream(dev))
+    ws = _WORKSPACES.get(key)
+    if ws is None or ws.numel() < nbytes:
+        size = max(int(nbytes), 1 << 20)
+        ws = torch.zeros(size, dtype=torch.uint8, device=dev)
+        _WORKSPACES[key] = ws
+    return ws
+
+
+def reset_workspaces() -> None:
+    """Drop all cached workspaces (after a reported device-side timeout the counters may be dirty)."""
+    _WORKSPACES.clear()
+
+
+class _dev_guard:
+    def __init__(self, dev: torch.device):
+        self.idx = dev.index if dev.index is not None else torch.cuda.current_device()
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.idx:
+            self.prev = cur
+            torch.cuda.set_device(self.idx)
+
+    def __exit__(self, *a):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+
+
+# ------------------------------------------------------------------------------------------------
+# dequant family
+# ------------------------------------------------------------------------------------------------
+def fp8_e4m3_to_fp16(x: torch.Tensor) -> torch.Tensor:
+    """uint8 E4M3 bytes -> flat float16 (reference op ``fp8_e4m3_to_fp16``, fp8_dequant.cu:129)."""
+    x = _as_u8(x)
+    dev = _require_cuda(x)
+    out = torch.empty(x.numel(), dtype=torch.float16, device=dev)
+    with _dev_guard(dev):
+        _cabi.check(_cabi.load().fp8w8a16_e4m3_to_fp16(x.data_ptr(), out.data_ptr(), x.numel(), _stream(dev)),
+                    "fp8w8a16_e4m3_to_fp16")
+    return out
+
+
+def fp8_e4m3_to_fp16_scaled(x: torch.Tensor, scales: torch.Tensor, group_size: int) -> torch.Tensor:
+    """Per-group scaled dequant (reference op ``fp8_e4m3_to_fp16_scaled``, fp8_dequant.cu:150)."""
+    x = _as_u8(x)
+    dev = _require_cuda(x, scales)
+    if scales.dtype != torch.float16:
+        raise RuntimeError("scales must be float16")
+    if scales.numel() * group_size < x.numel():
+        raise RuntimeError("not enough scales for the given group size")
+    out = torch.empty(x.numel(), dtype=torch.float16, device=dev)
+    with _dev_guard(dev):
+        _cabi.check(_cabi.load().fp8w8a16_e4m3_to_fp16_scaled(x.data_ptr(), scales.data_ptr(), out.data_ptr(), x.numel(),
+                                                               int(group_size), _stream(dev)),
+                    "fp8w8a16_e4m3_to_fp16_scaled")
+    return out
+
+
+def fp8_e4m3_to_fp16_block_scaled(w: torch.Tensor, scales: torch.Tensor, N: int, K: int, block_h: int = 128,
+                                  block_w: int = 128) -> torch.Tensor:
+    """Bit-exact dequantised weight, float16 [N, K] (reference op ``fp8_e4m3_to_fp16_block_scaled``,
+    fp8_dequant.cu:3053)."""
+    w = _as_u8(w)
+    dev = _require_cuda(w, scales)
+    if w.numel() != N * K:
+        raise RuntimeError(f"weight has {w.numel()} elements, expected N*K={N * K}")
+    nb, kb = -(-N // block_h), -(-K // block_w)
+    if scales.numel() != nb * kb:
+        raise RuntimeError(f"scales have {scales.numel()} elements, expected {nb}x{kb}")
+    out = torch.empty((N, K), dtype=torch.float16, device=dev)
+    with _dev_guard(dev):
+        _cabi.check(_cabi.load().fp8w8a16_dequant_block_scaled(w.data_ptr(), scales.data_ptr(), _scale_dtype(scales),
+                                                                out.data_ptr(), N, K, block_h, block_w, _stream(dev)),
+                    "fp8w8a16_dequant_block_scaled")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# dense W8A16 linear
+# ------------------------------------------------------------------------------------------------
+def w8a16_linear(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, N: int, K: int, block_h: int = 128,
+                 block_w: int = 128, algo: int = ALGO_AUTO, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x float16 [M, K] @ dequant(w [N, K], scales)^T -> float16 [M, N].
+
+    One op for the reference's dense family (gemv_coalesced, gemv_coalesced_m, gemm_a1/a2/a3,
+    gemm_wmma_poc) and the dispatch among them (src/fp8_w8a16_sm70/vllm_serve.py:1032-1100)."""
+    w = _as_u8(w)
+    dev = _require_cuda(x, w, scales)
+    if x.dtype != torch.float16:
+        raise RuntimeError(f"x must be float16 (got {x.dtype})")
+    if x.dim() != 2 or x.shape[1] != K:
+        raise RuntimeError(f"x must be [M, {K}] (got {tuple(x.shape)})")
+    if w.numel() != N * K:
+        raise RuntimeError(f"weight has {w.numel()} elements, expected N*K={N * K}")
+    nb, kb = -(-N // block_h), -(-K // block_w)
+    if scales.numel() != nb * kb:
+        raise RuntimeError(f"scales have {scales.numel()} elements, expected {nb}x{kb}")
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=dev)
+    lib = _cabi.load()
+    with _dev_guard(dev):
+        ws = workspace(dev, lib.fp8w8a16_linear_workspace_bytes(M, N, K))
+        _cabi.check(lib.fp8w8a16_linear(x.data_ptr(), w.data_ptr(), scales.data_ptr(), _scale_dtype(scales), out.data_ptr(),
+                                        M, N, K, block_h, block_w, algo, ws.data_ptr(), ws.numel(), _stream(dev)),
+                    "fp8w8a16_linear")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# MoE
+# ------------------------------------------------------------------------------------------------
+_LOGIT_DTYPES = {torch.float32: _cabi.DTYPE_F32, torch.float16: _cabi.DTYPE_F16, torch.bfloat16: _cabi.DTYPE_BF16}
+
+
+def moe_topk_softmax(logits: torch.Tensor, topk: int, renormalize: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Router logits [M, E] -> (topk_weights fp32 [M, topk], topk_ids int32 [M, topk])."""
+    dev = _require_cuda(logits)
+    if logits.dtype not in _LOGIT_DTYPES:
+        raise RuntimeError(f"unsupported logits dtype {logits.dtype}")
+    M, E = logits.shape
+    ids = torch.empty((M, topk), dtype=torch.int32, device=dev)
+    wts = torch.empty((M, topk), dtype=torch.float32, device=dev)
+    with _dev_guard(dev):
+        _cabi.check(_cabi.load().fp8w8a16_moe_topk_softmax(logits.data_ptr(), _LOGIT_DTYPES[logits.dtype], M, E, topk,
+                                                            1 if renormalize else 0, ids.data_ptr(), wts.data_ptr(),
+                                                            _stream(dev)),
+                    "fp8w8a16_moe_topk_softmax")
+    return wts, ids
+
+
+def moe_token_tile(R: int, num_local_experts: int) -> int:
+    return int(_cabi.load().fp8w8a16_moe_token_tile(R, num_local_experts))
+
+
+def moe_align(topk_ids: torch.Tensor, num_local_experts: int, token_tile: int, expert_map: Optional[torch.Tensor] = None):
+    """Route table: (counts [E], offsets [E+1], tile_offsets [E+1], sorted_route [R], inv_pos [R]), all int32."""
+    dev = _require_cuda(topk_ids)
+    if topk_ids.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("topk_ids must be int32 or int64")
+    R, E = topk_ids.numel(), num_local_experts
+    counts = torch.empty(E, dtype=torch.int32, device=dev)
+    offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    tile_offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+    sorted_route = torch.empty(R, dtype=torch.int32, device=dev)
+    inv_pos = torch.empty(R, dtype=torch.int32, device=dev)
+    emap_ptr, n_global = None, E
+    if expert_map is not None:
+        _require_cuda(topk_ids, expert_map)
+        if expert_map.dtype != torch.int32:
+            raise RuntimeError("expert_map must be int32")
+        emap_ptr, n_global = expert_map.data_ptr(), expert_map.numel()
+    with _dev_guard(dev):
+        _cabi.check(_cabi.load().fp8w8a16_moe_align(topk_ids.data_ptr(), 1 if topk_ids.dtype == torch.int64 else 0, R,
+                                                     emap_ptr, n_global, E, token_tile, counts.data_ptr(),
+                                                     offsets.data_ptr(), tile_offsets.data_ptr(), sorted_route.data_ptr(),
+                                                     inv_pos.data_ptr(), _stream(dev)),
+                    "fp8w8a16_moe_align")
+    return counts, offsets, tile_offsets, sorted_route, inv_pos
+
+
+def moe_gather(x: torch.Tensor, sorted_route: torch.Tensor, topk_weights: torch.Tensor, topk: int,
+               weight_on_input: bool = False):
+    dev = _require_cuda(x, sorted_route, topk_weights)
+    R, H = sorted_route.numel(), x.shape[1]
+    xs = torch.empty((R, H), dtype=torch.float16, device=dev)
+    wsorted = torch.empty(R, dtype=torch.float32, device=dev)
+    with _dev_guard(dev):
+        _cabi.check(_cabi.load().fp8w8a16_moe_gather(x.data_ptr(), sorted_route.data_ptr(), topk_weights.data_ptr(), R, topk, H,
+                                                      1 if weight_on_input else 0, xs.data_ptr(), wsorted.data_ptr(),
+                                                      _stream(dev)),
+                    "fp8w8a16_moe_gather")
+    return xs, wsorted
+
+
+def moe_combine(y_sorted: torch.Tensor, inv_pos: torch.Tensor, M: int, topk: int) -> torch.Tensor:
+    dev = _require_cuda(y_sorted, inv_pos)
+    H = y_sorted.shape[1]
+    out = torch.empty((M, H), dtype=torch.float16, device=dev)
+    with _dev_guard(dev):
+        _cabi.check(_cabi.load().fp8w8a16_moe_combine(y_sorted.data_ptr(), inv_pos.data_ptr(), M, topk, H, out.data_ptr(),
+                                                       _stream(dev)),
+                    "fp8w8a16_moe_combine")
+    return out
+
+
+def moe_grouped_gemm(x_sorted: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, offsets: torch.Tensor,
+                     tile_offsets: torch.Tensor, N: int, K: int, block_h: int, token_tile: int, paired: bool = False,
+                     row_weight: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Grouped expert GEMM over expert-sorted rows; ``paired`` fuses SiLU(gate) * up of a [E, 2N, K] weight."""
+    w = _as_u8(w)
+    dev = _require_cuda(x_sorted, w, scales, offsets, tile_offsets)
+    if x_sorted.dtype != torch.float16 or x_sorted.shape[1] != K:
+        raise RuntimeError(f"x_sorted must be float16 [R, {K}]")
+    E = w.shape[0]
+    rows_w = 2 * N if paired else N
+    if tuple(w.shape) != (E, rows_w, K):
+        raise RuntimeError(f"weight must be [{E}, {rows_w}, {K}] (got {tuple(w.shape)})")
+    R = x_sorted.shape[0]
+    out = torch.empty((R, N), dtype=torch.float16, device=dev)
+    lib = _cabi.load()
+    with _dev_guard(dev):
+        ws = workspace(dev, lib.fp8w8a16_moe_grouped_gemm_workspace_bytes(R, E, N, K, 1 if paired else 0, token_tile))
+        _cabi.check(lib.fp8w8a16_moe_grouped_gemm(x_sorted.data_ptr(), w.data_ptr(), scales.data_ptr(), _scale_dtype(scales),
+                                                  out.data_ptr(), None if row_weight is None else row_weight.data_ptr(),
+                                                  offsets.data_ptr(), tile_offsets.data_ptr(), R, E, N, K, block_h,
+                                                  1 if paired else 0, token_tile, ws.data_ptr(), ws.numel(), _stream(dev)),
+                    "fp8w8a16_moe_grouped_gemm")
+    return out
+
+
+def moe_forward(x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor, w13: torch.Tensor, s13: torch.Tensor,
+                w2: torch.Tensor, s2: torch.Tensor, block_h: int = 128, expert_map: Optional[torch.Tensor] = None,
+                weight_on_input: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Routed-only MoE layer output float16 [M, H] (reference: ``_our_moe_apply``,
+    src/fp8_w8a16_sm70/vllm_serve.py:2175-2411)."""
+    w13, w2 = _as_u8(w13), _as_u8(w2)
+    dev = _require_cuda(x, topk_weights, topk_ids, w13, s13, w2, s2)
+    if x.dtype != torch.float16:
+        raise RuntimeError("x must be float16")
+    if topk_weights.dtype != torch.float32:
+        raise RuntimeError("topk_weights must be float32")
+    if topk_ids.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("topk_ids must be int32 or int64")
+    if s13.dtype != s2.dtype:
+        raise RuntimeError("w13 and w2 scales must share a dtype")
+    M, H = x.shape
+    E, two_i, h2 = w13.shape
+    I = two_i // 2
+    if h2 != H or tuple(w2.shape) != (E, H, I):
+        raise RuntimeError(f"shape mismatch: x {tuple(x.shape)}, w13 {tuple(w13.shape)}, w2 {tuple(w2.shape)}")
+    topk = topk_ids.shape[-1]
+    if topk_ids.numel() != M * topk or topk_weights.numel() != M * topk:
+        raise RuntimeError("topk_ids / topk_weights must be [M, topk]")
+    kb13, kb2 = -(-H // 128), -(-I // 128)
+    if s13.numel() != E * (-(-two_i // block_h)) * kb13 or s2.numel() != E * (-(-H // block_h)) * kb2:
+        raise RuntimeError("scale grid size does not match the weights and block_h")
+    emap_ptr, n_global = None, E
+    if expert_map is not None:
+        _require_cuda(x, expert_map)
+        if expert_map.dtype != torch.int32:
+            raise RuntimeError("expert_map must be int32")
+        emap_ptr, n_global = expert_map.data_ptr(), expert_map.numel()
+    if out is None:
+        out = torch.empty((M, H), dtype=torch.float16, device=dev)
+    lib = _cabi.load()
+    with _dev_guard(dev):
+        ws = workspace(dev, lib.fp8w8a16_moe_workspace_bytes(M, topk, E, H, I))
+        _cabi.check(lib.fp8w8a16_moe_forward(x.data_ptr(), topk_ids.data_ptr(), 1 if topk_ids.dtype == torch.int64 else 0,
+                                             topk_weights.data_ptr(), emap_ptr, n_global, w13.data_ptr(), s13.data_ptr(),
+                                             w2.data_ptr(), s2.data_ptr(), _scale_dtype(s13), out.data_ptr(), M, topk, E, H, I,
+                                             block_h, 1 if weight_on_input else 0, ws.data_ptr(), ws.numel(), _stream(dev)),
+                    "fp8w8a16_moe_forward")
+    return out
+
+
+def device_status(reset: bool = True) -> int:
+    """Sticky device status word (0 = healthy).  Synchronises the device."""
+    return _cabi.device_status(reset)
