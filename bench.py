@@ -1,0 +1,492 @@
+#!/usr/bin/env python
+"""Benchmark of the FP8 W8A16 hot path on B200.
+
+Default workload ("decode", the configuration the headline metric is quoted on): the dense decode
+sweep of a 64-layer 5120-hidden / 25600-FFN decoder — qkv [7168,5120], o_proj [5120,5120],
+gate_up [51200,5120], down [5120,25600], block-128 E4M3 weights, FP16 activations, M in
+{1,2,4,8,16,32,64}.  One step = one pass over the four linears at all seven M (28 GEMMs).
+value = algorithmic bytes (weights + scales + activations + outputs) / device time, in GB/s.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload decode|prefill|moe]
+
+N > 1 (launched with torch.distributed.run): dense layers are tensor-parallel (column-parallel qkv /
+gate_up, row-parallel o_proj / down + NCCL all-reduce), MoE is expert-parallel (all-to-all).
+Prints ONE JSON line on rank 0.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+DENSE_SHAPES = [("qkv", 7168, 5120, "column"), ("o_proj", 5120, 5120, "row"), ("gate_up", 51200, 5120, "column"),
+                ("down", 5120, 25600, "row")]
+DECODE_M = [1, 2, 4, 8, 16, 32, 64]
+PREFILL_M = [512, 2048, 8192]
+MOE_CFG = dict(E=128, topk=8, H=2048, I=768)
+NOMINAL_HBM_GBS = 8000.0
+NOMINAL_F16_TFLOPS = 2250.0
+
+
+def algorithmic_bytes(M: int, N: int, K: int, block_h: int = 128) -> int:
+    """N*K (fp8 W) + 4*ceil(N/bh)*ceil(K/128) (fp32 scales) + 2*M*K (x) + 2*M*N (y)."""
+    return N * K + 4 * (-(-N // block_h)) * (-(-K // 128)) + 2 * M * K + 2 * M * N
+
+
+def measured_peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "tflops": float(d["bf16_tflops"]), "tflops_sustained": float(d["bf16_tflops_sustained"]),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200",
+                                          "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[3:7]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def synth_block_fp8(N: int, K: int, seed: int, device) -> tuple:
+    """W ~ N(0, 0.02) quantised per 128x128 block, s = blockmax / 448 (fp32), Wq = (W/s) as E4M3.  Generated on the
+    device from a seeded generator (synthetic stand-in for a checkpoint)."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    w = torch.randn(N, K, generator=g, device=device, dtype=torch.float32) * 0.02
+    blocks = w.reshape(N // 128, 128, K // 128, 128)
+    s = blocks.abs().amax(dim=(1, 3)) / 448.0
+    q = (blocks / s[:, None, :, None]).reshape(N, K).to(torch.float8_e4m3fn).view(torch.uint8).contiguous()
+    return q, s.contiguous()
+
+
+def dist_setup(n_gpus: int):
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    else:
+        torch.cuda.set_device(0)
+    return world, rank, local
+
+
+def barrier_sync(world: int):
+    if world > 1:
+        import torch.distributed as dist
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms: float, world: int) -> float:
+    if world == 1:
+        return ms
+    import torch.distributed as dist
+    t = torch.tensor([ms], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+class Flusher:
+    """Writes a buffer larger than the 126 MB L2 between individually timed calls."""
+
+    def __init__(self, device):
+        self.buf = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+
+    def __call__(self):
+        self.buf.fill_(1)
+
+
+def time_call(fn, reps: int, flush) -> float:
+    """Mean device milliseconds of fn(), each repetition individually bracketed by events after an L2 flush."""
+    total = 0.0
+    for _ in range(reps):
+        flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        total += a.elapsed_time(b)
+    return total / reps
+
+
+# ------------------------------------------------------------------------------------------------
+# dense layers (decode / prefill)
+# ------------------------------------------------------------------------------------------------
+class DenseStack:
+    """`layers` copies of the four linears of one decoder layer; with world > 1 every rank holds its TP shard."""
+
+    def __init__(self, layers: int, world: int, rank: int, device):
+        from vllm_fp8_w8a16_sm70_b200 import parallel as par
+        self.world, self.device = world, device
+        self.layers = []
+        for li in range(layers):
+            lin = {}
+            for si, (name, N, K, mode) in enumerate(DENSE_SHAPES):
+                q, s = synth_block_fp8(N, K, 1000 * li + si, device)
+                s16 = s.to(torch.float16)        # load-time cast, as process_weights_after_loading does
+                if world > 1:
+                    q, s16 = (par.shard_column_parallel if mode == "column" else par.shard_row_parallel)(q, s16, world, rank)
+                lin[name] = par.TensorParallelLinear(q, s16, 128, mode)
+                del s
+            self.layers.append(lin)
+        torch.cuda.empty_cache()
+
+    def inputs(self, M: int, seed: int = 0):
+        g = torch.Generator(device=self.device).manual_seed(seed + M)
+        return {name: torch.randn(M, lin.K, generator=g, device=self.device).to(torch.float16)
+                for name, lin in self.layers[0].items()}
+
+
+def run_dense(args, world, rank, local, m_list, workload: str) -> dict:
+    from vllm_fp8_w8a16_sm70_b200 import _cabi, ops
+    device = torch.device("cuda", local)
+    peaks = measured_peaks()
+    n_layers = 2 if workload == "decode" else 1
+    stack = DenseStack(n_layers, world, rank, device)
+    xs = {M: stack.inputs(M) for M in m_list}
+    lib = _cabi.load()
+
+    def step(i: int):
+        lay = stack.layers[i % n_layers]
+        for M in m_list:
+            for name, _, _, _ in DENSE_SHAPES:
+                lay[name].forward(xs[M][name])
+
+    bytes_step = sum(algorithmic_bytes(M, N, K) for M in m_list for _, N, K, _ in DENSE_SHAPES)
+    flops_step = sum(2 * M * N * K for M in m_list for _, N, K, _ in DENSE_SHAPES)
+    for i in range(args.warmup):
+        step(i)
+    barrier_sync(world)
+    launches0 = lib.fp8w8a16_launch_count()
+    with ClockSampler(local) as clk:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for i in range(args.steps):
+            step(i)
+        b.record()
+        barrier_sync(world)
+        ms_total = max_over_ranks(a.elapsed_time(b), world)
+    launches = lib.fp8w8a16_launch_count() - launches0
+    ms_step = ms_total / args.steps
+
+    # ---- end to end through the plugin-shaped API with HOST buffers ----
+    e2e = run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, workload)
+
+    # ---- per-case device times (rank-local, L2 flushed between calls) for the roofline ----
+    cases, flush = [], Flusher(device)
+    reps = 5 if workload == "decode" else 2
+    for M in m_list:
+        for name, N, K, _ in DENSE_SHAPES:
+            lin = stack.layers[0][name]
+            ms = time_call(lambda: lin.forward(xs[M][name]), reps, flush)
+            nb = algorithmic_bytes(M, lin.N, lin.K)
+            cases.append({"layer": name, "M": M, "ms": round(ms, 5), "GBps": round(nb / ms / 1e6, 1),
+                          "TFLOPs": round(2 * M * lin.N * lin.K / ms / 1e9, 2), "kernel": "gemv" if M <= 4 else "gemm_tc"})
+    st = ops.device_status(reset=True)
+    if st != 0:
+        raise RuntimeError(f"device status word {st:#x}: a kernel timed out on a bounded wait")
+
+    if workload == "decode":
+        dom = "gemm_tc"
+        sel = [c for c in cases if c["kernel"] == dom]
+        ach = sum(algorithmic_bytes(c["M"], *shape_of(stack, c["layer"])) for c in sel) / sum(c["ms"] for c in sel) / 1e6
+        roof = {"bound": "hbm", "kernel": "k_gemm_tc (tcgen05 W8A16, decode tiles)", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"],
+                "unit": "GB/s", "frac": round(ach / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
+                "frac_of_nominal_8TBps": round(ach / NOMINAL_HBM_GBS, 4), "traffic": None}
+        value, unit, metric = bytes_step * world_factor(world) / ms_step / 1e6, "GB/s", "w8a16_decode_gemv_hbm_GBps"
+    else:
+        ach = sum(2 * c["M"] * shape_of(stack, c["layer"])[0] * shape_of(stack, c["layer"])[1] for c in cases) / sum(c["ms"] for c in cases) / 1e9
+        roof = {"bound": "tensor", "kernel": "k_gemm_tc (tcgen05 W8A16, prefill tiles)", "achieved": round(ach, 1),
+                "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "frac": round(ach / peaks["tflops_sustained"], 4),
+                "peak_source": peaks["source"] + " (sustained bf16 matmul)", "frac_of_nominal_2250": round(ach / NOMINAL_F16_TFLOPS, 4),
+                "traffic": None}
+        value, unit, metric = flops_step * world_factor(world) / ms_step / 1e9, "TFLOP/s", "w8a16_prefill_gemm_TFLOPs"
+    out = {
+        "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic", "impl": "ours",
+        "config": {"workload": f"dense {workload} sweep: qkv[7168,5120] o[5120,5120] gate_up[51200,5120] down[5120,25600], block-128 "
+                               f"E4M3 + block scales, fp16 acts, M in {m_list}", "parallelism": f"tp{world}",
+                   "l2": "weights cycled: 456 MB per layer pass x %d layer copies > 126 MB L2; per-case timings flush L2" % n_layers},
+        "roofline": roof, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk.summary(), "cases": cases,
+    }
+    return out
+
+
+def shape_of(stack, name):
+    lin = stack.layers[0][name]
+    return lin.N, lin.K
+
+
+def world_factor(world: int) -> int:
+    # bytes_step / flops_step are computed from the FULL layer shapes, so the whole-job figure needs no scaling
+    return 1
+
+
+def run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, workload) -> dict:
+    """Same sweep through Fp8LinearMethod.apply with pinned HOST activations in and HOST results out every call."""
+    from vllm_fp8_w8a16_sm70_b200 import Fp8LinearMethod
+    import types
+    method = Fp8LinearMethod((128, 128))
+    layers = []
+    for lay in stack.layers:
+        objs = {}
+        for name, lin in lay.items():
+            objs[name] = types.SimpleNamespace(weight=lin.w, weight_scale_inv=lin.s, weight_block_size=[128, 128],
+                                               input_size_per_partition=lin.K, output_size_per_partition=lin.N, mode=lin.mode)
+        layers.append(objs)
+    host_x = {M: {n: torch.randn(M, layers[0][n].input_size_per_partition).to(torch.float16).pin_memory() for n in layers[0]} for M in m_list}
+    host_y = {M: {n: torch.empty(M, layers[0][n].output_size_per_partition, dtype=torch.float16).pin_memory() for n in layers[0]} for M in m_list}
+    h2d = sum(t.numel() * 2 for M in m_list for t in host_x[M].values())
+    d2h = sum(t.numel() * 2 for M in m_list for t in host_y[M].values())
+
+    def step(i):
+        lay = layers[i % len(layers)]
+        for M in m_list:
+            for name in lay:
+                x = host_x[M][name].to(device, non_blocking=True)
+                y = method.apply(lay[name], x)
+                if lay[name].mode == "row" and world > 1:
+                    import torch.distributed as dist
+                    dist.all_reduce(y)
+                host_y[M][name].copy_(y, non_blocking=True)
+    for i in range(max(1, args.warmup)):
+        step(i)
+    barrier_sync(world)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(args.steps):
+        step(i)
+    b.record()
+    barrier_sync(world)
+    ms = max_over_ranks(a.elapsed_time(b), world) / args.steps
+    if workload == "decode":
+        return {"value": round(bytes_step / ms / 1e6, 2), "unit": "GB/s", "ms_per_step": round(ms, 4), "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "api": "Fp8LinearMethod.apply"}
+    return {"value": round(flops_step / ms / 1e9, 2), "unit": "TFLOP/s", "ms_per_step": round(ms, 4), "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "api": "Fp8LinearMethod.apply"}
+
+
+# ------------------------------------------------------------------------------------------------
+# MoE decode layer
+# ------------------------------------------------------------------------------------------------
+def run_moe(args, world, rank, local, m_list=(1, 8, 64, 256)) -> dict:
+    from vllm_fp8_w8a16_sm70_b200 import _cabi, ops, parallel as par
+    device = torch.device("cuda", local)
+    E, topk, H, I = MOE_CFG["E"], MOE_CFG["topk"], MOE_CFG["H"], MOE_CFG["I"]
+    per = E // world
+    g = torch.Generator(device=device).manual_seed(7)
+    w13 = torch.empty(per, 2 * I, H, dtype=torch.uint8, device=device)
+    w2 = torch.empty(per, H, I, dtype=torch.uint8, device=device)
+    s13 = torch.empty(per, 2 * I // 128, H // 128, dtype=torch.float16, device=device)
+    s2 = torch.empty(per, H // 128, I // 128, dtype=torch.float16, device=device)
+    for e in range(per):
+        q, s = synth_block_fp8(2 * I, H, 100 + rank * per + e, device)
+        w13[e], s13[e] = q, s.to(torch.float16)
+        q, s = synth_block_fp8(H, I, 5000 + rank * per + e, device)
+        w2[e], s2[e] = q, s.to(torch.float16)
+    layer = par.ExpertParallelMoE(w13, s13, w2, s2, E) if world > 1 else None
+    lib = _cabi.load()
+    results = []
+    for M in m_list:
+        x = torch.randn(M, H, generator=g, device=device).to(torch.float16)
+        logits = torch.randn(M, E, generator=g, device=device)
+
+        def step():
+            tw, ids = ops.moe_topk_softmax(logits, topk, True)
+            if world > 1:
+                return layer.forward(x, tw, ids)
+            return ops.moe_forward(x, tw, ids, w13, s13, w2, s2, block_h=128)
+        for _ in range(max(3, args.warmup)):
+            step()
+        barrier_sync(world)
+        n0 = lib.fp8w8a16_launch_count()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(args.steps):
+            step()
+        b.record()
+        barrier_sync(world)
+        ms = max_over_ranks(a.elapsed_time(b), world) / args.steps
+        tw, ids = ops.moe_topk_softmax(logits, topk, True)
+        distinct = int(torch.unique(ids).numel())
+        nbytes = distinct * (3 * I * H + 4 * (2 * I // 128 * H // 128 + H // 128 * I // 128)) + 2 * M * H * 2 + 4 * M * E
+        results.append({"M_per_gpu": M, "tok_per_s": round(world * M / ms * 1e3, 1), "ms": round(ms, 4), "distinct_experts": distinct,
+                        "GBps_active_experts": round(nbytes / ms / 1e6, 1), "launches_per_step": int((lib.fp8w8a16_launch_count() - n0) / args.steps)})
+    st = ops.device_status(reset=True)
+    if st != 0:
+        raise RuntimeError(f"device status word {st:#x}")
+    return {"config": "MoE decode layer: E=128 top-8 softmax routing, H=2048, I=768, block-128 E4M3, fp16 acts; "
+                      f"ep{world} all-to-all" if world > 1 else "MoE decode layer: E=128 top-8 softmax routing, H=2048, I=768, block-128 E4M3, fp16 acts",
+            "weights_MB_in_L2_note": "604 MB of expert weights per GPU at ep1 > 126 MB L2", "results": results}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline: the reference's torch dequant-then-matmul path on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_reference_sample(threads: int, reps: int = 3) -> dict:
+    """Reference CPU path (compressed_tensors_v100.py:231-270 + F.linear) on a bounded sample of the decode sweep:
+    o_proj [5120,5120] and qkv [7168,5120] at M = 1 and M = 16.  Returns GB/s in the benchmark's metric."""
+    from oracle import linear as olin
+    torch.set_num_threads(threads)
+    g = torch.Generator().manual_seed(0)
+    total_b, total_s, dq_s, mm_s = 0, 0.0, 0.0, 0.0
+    for name, N, K in (("o_proj", 5120, 5120), ("qkv", 7168, 5120)):
+        w = torch.randn(N, K, generator=g) * 0.02
+        q, s = olin.quantize_block_fp8(w)
+        for M in (1, 16):
+            x = torch.randn(M, K, generator=g).to(torch.float16)
+            olin.reference_cpu_linear(x, q, s)          # warm-up
+            for _ in range(reps):
+                t0 = time.perf_counter()
+                wdq = olin.dequant_weight_torch(q, s, 128, 128)
+                t1 = time.perf_counter()
+                torch.nn.functional.linear(x, wdq)
+                t2 = time.perf_counter()
+                dq_s += t1 - t0
+                mm_s += t2 - t1
+                total_s += t2 - t0
+                total_b += algorithmic_bytes(M, N, K)
+    return {"value": round(total_b / total_s / 1e9, 3), "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": f"o_proj[5120,5120] + qkv[7168,5120] at M in (1,16), {reps} reps each; dequant {dq_s:.2f} s + matmul {mm_s:.2f} s",
+            "note": "oracle/linear.py restatement of the reference's torch dequant-then-matmul path"}
+
+
+def run_reference_arm(args) -> None:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    threads = os.cpu_count() or 1
+    for _ in range(max(0, min(args.warmup, 1))):
+        cpu_reference_sample(threads, reps=1)
+    t0 = time.perf_counter()
+    vals = [cpu_reference_sample(threads, reps=1) for _ in range(args.steps)]
+    dt = time.perf_counter() - t0
+    v = statistics.mean(x["value"] for x in vals)
+    cb = dict(vals[-1], value=round(v, 3))
+    print(json.dumps({
+        "metric": "w8a16_decode_gemv_hbm_GBps", "value": round(v, 3), "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(dt / args.steps * 1e3, 2), "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic", "impl": "reference",
+        "config": {"workload": "bounded sample of the dense decode sweep on the host CPU: o_proj[5120,5120] + qkv[7168,5120] at M in (1,16)",
+                   "parallelism": "cpu"},
+        "cpu_baseline": cb, "e2e": {"value": round(v, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe"])
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill / MoE side measurements")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+        return
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device (the engine has no CPU path); use --impl reference for the CPU arm")
+    world, rank, local = dist_setup(args.gpus)
+    if args.workload == "decode":
+        out = run_dense(args, world, rank, local, DECODE_M, "decode")
+    elif args.workload == "prefill":
+        out = run_dense(args, world, rank, local, PREFILL_M if world == 1 else PREFILL_M, "prefill")
+    else:
+        moe = run_moe(args, world, rank, local)
+        best = max(moe["results"], key=lambda r: r["tok_per_s"])
+        out = {"metric": "moe_decode_layer_tok_per_s", "value": best["tok_per_s"], "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+               "warmup": args.warmup, "ms_per_step": best["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+               "dtype": "f16", "data": "synthetic", "impl": "ours", "config": {"workload": moe["config"], "parallelism": f"ep{world}"},
+               "moe": moe}
+    if args.workload == "decode" and not args.no_extras:
+        extra = {}
+        torch.cuda.empty_cache()
+        try:
+            sub = argparse.Namespace(**vars(args))
+            sub.steps, sub.warmup = 2, 3
+            pre = run_dense(sub, world, rank, local, [2048], "prefill")
+            extra["prefill_M2048"] = {"TFLOPs": pre["value"], "roofline": pre["roofline"], "cases": pre["cases"]}
+        except Exception as e:  # the headline line must still be printed
+            extra["prefill_M2048"] = {"error": repr(e)[:300]}
+        torch.cuda.empty_cache()
+        try:
+            sub = argparse.Namespace(**vars(args))
+            sub.steps = 20
+            extra["moe_decode"] = run_moe(sub, world, rank, local)
+        except Exception as e:
+            extra["moe_decode"] = {"error": repr(e)[:300]}
+        out["extra"] = extra
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        out["cpu_baseline"] = cpu_reference_sample(os.cpu_count() or 1, reps=3)
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        import torch.distributed as dist
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

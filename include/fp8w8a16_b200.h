@@ -47,6 +47,10 @@ extern "C" {
 int fp8w8a16_version(void);
 const char* fp8w8a16_last_error(void);
 
+/* Number of kernels this library has launched in this process (a host-side counter; used by the
+ * benchmark to report how many of its own kernels ran inside a timed region). */
+uint64_t fp8w8a16_launch_count(void);
+
 /* Sticky device status word (bit set = a bounded wait inside a kernel gave up).  Synchronises the
  * device.  *status (host) receives the bits; reset != 0 clears them. */
 int fp8w8a16_device_status(int* status, int reset);

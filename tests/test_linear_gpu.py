@@ -1,0 +1,142 @@
+"""GPU parity of the dense W8A16 linear against the fp32-accumulate oracle, through the C ABI.
+Tolerance: max-abs-err <= 2e-3 * ||x||inf * sqrt(K) and relative RMS <= 1e-2 (oracle.linear.check_linear)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import linear as olin, tp as otp
+from tests.helpers import bits, f16_from_bits, make_dense
+
+pytestmark = pytest.mark.gpu
+GEMV, TC = 1, 2
+
+
+@pytest.fixture(scope="module")
+def ops(lib):
+    from vllm_fp8_w8a16_sm70_b200 import ops as _ops
+    return _ops
+
+
+def run(ops, x, w, s, bh, algo):
+    N, K = w.shape
+    return ops.w8a16_linear(x.cuda(), w.cuda(), s.cuda(), N, K, bh, 128, algo=algo).cpu()
+
+
+@pytest.mark.parametrize("algo", [GEMV, TC])
+@pytest.mark.parametrize("M", [1, 2, 3, 4, 5, 8, 16, 17, 32, 63, 64, 65, 100, 128, 200, 300, 512])
+def test_block_scaled_M_sweep(ops, M, algo):
+    # M list: reference tests/test_wmma_dispatch.py:90-124 plus the decode sweep
+    if algo == GEMV and M > 17:
+        pytest.skip("GEMV path is for decode batches")
+    x, w, s, bh = make_dense(M, 640, 1536, seed=M)
+    y = run(ops, x, w, s, bh, algo)
+    olin.check_linear(y, x, olin.oracle_linear_fp32(x, w, s, bh), 1536)
+
+
+@pytest.mark.parametrize("algo", [GEMV, TC])
+@pytest.mark.parametrize("N,K", [(352, 512), (2736, 256), (128, 16), (8, 4096), (130, 144), (5120, 5120)])
+@pytest.mark.parametrize("M", [1, 7, 33])
+def test_odd_shapes_block(ops, N, K, M, algo):
+    # partial-N shapes of the reference numtests: 352, 2736
+    if algo == GEMV and M > 8:
+        pytest.skip("GEMV path is for decode batches")
+    x, w, s, bh = make_dense(M, N, K, seed=N + K)
+    y = run(ops, x, w, s, bh, algo)
+    olin.check_linear(y, x, olin.oracle_linear_fp32(x, w, s, bh), K)
+
+
+@pytest.mark.parametrize("algo", [GEMV, TC])
+@pytest.mark.parametrize("N,K", [(4096, 176), (352, 4096), (1792, 512)])
+@pytest.mark.parametrize("M", [1, 4, 40])
+def test_channel_scales_and_K176(ops, N, K, M, algo):
+    if algo == GEMV and M > 8:
+        pytest.skip("GEMV path is for decode batches")
+    x, w, s, bh = make_dense(M, N, K, seed=7, scheme="channel")
+    assert bh == 1
+    y = run(ops, x, w, s, bh, algo)
+    olin.check_linear(y, x, olin.oracle_linear_fp32(x, w, s, bh), K)
+
+
+@pytest.mark.parametrize("algo", [GEMV, TC])
+def test_fp32_scales_are_rounded_to_fp16_like_the_reference(ops, algo):
+    x, w, s32, bh = make_dense(4, 256, 512, seed=11)
+    y32 = run(ops, x, w, s32, bh, algo)
+    y16 = run(ops, x, w, s32.to(torch.float16), bh, algo)
+    assert torch.equal(y32.view(torch.int16), y16.view(torch.int16))
+
+
+@pytest.mark.parametrize("algo", [GEMV, TC])
+def test_golden_fixtures(ops, golden_dir, algo):
+    z = np.load(golden_dir / "dense_reference.npz")
+    for tag in "abc":
+        x, w, s16 = f16_from_bits(z[f"{tag}_x"]), torch.from_numpy(z[f"{tag}_w"]), f16_from_bits(z[f"{tag}_s16"])
+        y = run(ops, x, w, s16, 128, algo)
+        ref16 = f16_from_bits(z[f"{tag}_y16"])
+        olin.check_linear(y, x, ref16.float(), w.shape[1])
+        # reference test bar (tests/test_phase5_matmul.py:164): max_abs <= 1e-2
+        assert float((y.float() - ref16.float()).abs().max()) <= 1e-2
+
+
+@pytest.mark.parametrize("algo", [GEMV, TC])
+def test_deterministic_and_workspace_self_cleaning(ops, algo):
+    x, w, s, bh = make_dense(3, 512, 4096, seed=2)   # small N, long K: split-K is taken
+    xs, ws, ss = x.cuda(), w.cuda(), s.cuda()
+    first = ops.w8a16_linear(xs, ws, ss, 512, 4096, bh, 128, algo=algo).clone()
+    for _ in range(5):
+        again = ops.w8a16_linear(xs, ws, ss, 512, 4096, bh, 128, algo=algo)
+        assert torch.equal(first.view(torch.int16), again.view(torch.int16))
+    olin.check_linear(first.cpu(), x, olin.oracle_linear_fp32(x, w, s, bh), 4096)
+
+
+def test_gemv_and_tensor_core_paths_agree(ops):
+    # the reference pins kernel-vs-kernel agreement at L2rel < 5e-3 (tools/ct_fp8_resident_numtest_vllm021.sh)
+    x, w, s, bh = make_dense(4, 1024, 2048, seed=9)
+    a, b = run(ops, x, w, s, bh, GEMV).float(), run(ops, x, w, s, bh, TC).float()
+    assert float((a - b).norm() / b.norm()) < 5e-3
+
+
+def test_tp_shards_through_engine(ops):
+    """vLLM TP=4 sharding emulated on one GPU (reference: tests/test_attention_shapes.py:75-101,199-296)."""
+    x, w, s, bh = make_dense(6, 1024, 2048, seed=4)
+    full = olin.oracle_linear_fp32(x, w, s, bh)
+    cols = [run(ops, x, *otp.shard_col_parallel(w, s, 4, r), bh, 0) for r in range(4)]
+    olin.check_linear(torch.cat(cols, 1), x, full, 2048)
+    acc = torch.zeros_like(full)
+    for r in range(4):
+        wr, sr = otp.shard_row_parallel(w, s, 4, r)
+        acc += run(ops, x[:, r * 512:(r + 1) * 512].contiguous(), wr, sr, bh, 0).float()
+    olin.check_linear(acc, x, full, 2048)
+
+
+@pytest.mark.parametrize("name,N,K", [("qkv", 7168, 5120), ("o_proj", 5120, 5120), ("down", 5120, 25600)])
+@pytest.mark.parametrize("M", [1, 16, 64])
+def test_full_size_decode_shapes_on_device(ops, name, N, K, M):
+    """Full decode-sweep shapes: compared on the device against the bit-exact dequant kernel followed by an
+    fp32 matmul (the reference's own test method, tests/test_phase5_matmul.py:88-175), plus linearity."""
+    g = torch.Generator(device="cuda").manual_seed(1)
+    w = (torch.randn(N, K, generator=g, device="cuda") * 0.02)
+    blocks = w.reshape(N // 128, 128, K // 128, 128)
+    s = blocks.abs().amax(dim=(1, 3)) / 448.0
+    q = (blocks / s[:, None, :, None]).reshape(N, K).to(torch.float8_e4m3fn).view(torch.uint8)
+    del w, blocks
+    x = torch.randn(M, K, generator=g, device="cuda").to(torch.float16)
+    wdq = ops.fp8_e4m3_to_fp16_block_scaled(q, s, N, K)
+    ref = x.float() @ wdq.float().T
+    del wdq
+    y = ops.w8a16_linear(x, q, s, N, K)
+    olin.check_linear(y.cpu(), x.cpu(), ref.cpu(), K)
+    y2 = ops.w8a16_linear((x * 2).to(torch.float16), q, s, N, K)      # exact in FP16: doubling commutes with every rounding
+    assert torch.equal((y.float() * 2).to(torch.float16).view(torch.int16), y2.view(torch.int16)) or \
+        float((y2.float() - 2 * y.float()).abs().max()) <= 2e-3 * float(y.abs().max())
+
+
+def test_errors_surface_as_runtime_error(ops):
+    x = torch.zeros(2, 100, dtype=torch.float16, device="cuda")
+    w = torch.zeros(128, 100, dtype=torch.uint8, device="cuda")
+    s = torch.ones(1, 1, dtype=torch.float16, device="cuda")
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        ops.w8a16_linear(x, w, s, 128, 100)
+    with pytest.raises(RuntimeError):
+        ops.w8a16_linear(x.float(), w, s, 128, 100)
+    assert ops.w8a16_linear(torch.zeros(0, 128, dtype=torch.float16, device="cuda"), torch.zeros(128, 128, dtype=torch.uint8, device="cuda"),
+                            s, 128, 128).shape == (0, 128)

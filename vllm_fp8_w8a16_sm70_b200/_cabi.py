@@ -22,6 +22,7 @@ ALGO_AUTO, ALGO_GEMV, ALGO_TC = 0, 1, 2
 PROTOTYPES = {
     "fp8w8a16_version": (c_int, []),
     "fp8w8a16_last_error": (c_char_p, []),
+    "fp8w8a16_launch_count": (ctypes.c_uint64, []),
     "fp8w8a16_device_status": (c_int, [POINTER(c_int), c_int]),
     "fp8w8a16_e4m3_to_fp16": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "fp8w8a16_e4m3_to_fp16_scaled": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),

@@ -3,6 +3,8 @@
 #include <stdarg.h>
 #include <string.h>
 
+#include <atomic>
+
 #include "common.cuh"
 #include "gemm_tc.h"
 
@@ -25,6 +27,9 @@ int fail(int code, const char* fmt, ...) {
     va_end(ap);
     return code;
 }
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 int sm_count() {
     static int cached[64] = {};
@@ -268,6 +273,8 @@ extern "C" {
 int fp8w8a16_version(void) { return 100; }
 
 const char* fp8w8a16_last_error(void) { return t_err; }
+
+uint64_t fp8w8a16_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int fp8w8a16_device_status(int* status, int reset) {
     W8A16_REQUIRE(status != nullptr, FP8W8A16_ERR_INVALID, "device_status: null status pointer");

@@ -29,9 +29,13 @@ int fail(int code, const char* fmt, ...);
             return ::w8a16::fail(FP8W8A16_ERR_CUDA, "%s failed: %s", #call, cudaGetErrorString(_e)); \
     } while (0)
 
+// Kernels launched by this library in this process (reported by fp8w8a16_launch_count).
+void count_launch();
+
 inline int check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail(FP8W8A16_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(e));
+    count_launch();
     return 0;
 }
 

@@ -1,0 +1,143 @@
+"""Tensor-parallel dense layers and expert-parallel MoE over ``torch.distributed`` (NCCL on GPUs).
+
+In the reference these collectives belong to vLLM: the plugin only sees per-rank shards
+(``src/fp8_w8a16_sm70/vllm_serve.py:1386-1387``) and mirrors vLLM's call sites for timing
+(row-parallel: split input, apply, all-reduce, bias on rank 0 only — ``vllm_serve.py:2922-2959``;
+MoE: experts, then reduce — ``:2785-2853``).  Expert parallelism is only *tolerated* there
+(``expert_map`` + a later reduce, ``:2237-2243``); the all-to-all dispatch / combine below is new,
+and its oracle is the single-GPU layer.
+
+One process per GPU.  Nothing here is a fused compute + collective kernel: the GEMMs are the
+engine's, the exchange is NCCL's.
+"""
+
+from __future__ import annotations
+
+from typing import Callable, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+
+from . import ops
+
+
+# ------------------------------------------------------------------------------------------------
+# sharding rules (what vLLM's loaders do to the FP8 weight and its block-scale grid)
+# ------------------------------------------------------------------------------------------------
+def shard_column_parallel(w: torch.Tensor, s: torch.Tensor, tp_size: int, tp_rank: int, block_h: int = 128):
+    """Cut along the output dimension: weight rows and scale-grid rows together."""
+    N = w.shape[0]
+    if N % tp_size:
+        raise ValueError(f"N={N} not divisible by tp_size={tp_size}")
+    n_per = N // tp_size
+    if n_per % block_h:
+        raise ValueError(f"per-rank N={n_per} is not a multiple of block_h={block_h}")
+    nb_per = n_per // block_h
+    return (w[tp_rank * n_per:(tp_rank + 1) * n_per].contiguous(), s[tp_rank * nb_per:(tp_rank + 1) * nb_per].contiguous())
+
+
+def shard_row_parallel(w: torch.Tensor, s: torch.Tensor, tp_size: int, tp_rank: int, block_w: int = 128):
+    """Cut along the input dimension: weight columns and scale-grid columns together."""
+    K = w.shape[1]
+    if K % tp_size:
+        raise ValueError(f"K={K} not divisible by tp_size={tp_size}")
+    k_per = K // tp_size
+    if k_per % block_w and s.shape[1] > 1:
+        # a per-rank K that is not 128-aligned needs per-channel scales (one grid column per started block)
+        raise ValueError(f"per-rank K={k_per} is not a multiple of block_w={block_w}")
+    kb_per = -(-k_per // block_w)
+    return (w[:, tp_rank * k_per:(tp_rank + 1) * k_per].contiguous(), s[:, tp_rank * kb_per:(tp_rank + 1) * kb_per].contiguous())
+
+
+class TensorParallelLinear:
+    """One rank's shard of a column- or row-parallel FP8 linear."""
+
+    def __init__(self, w_shard: torch.Tensor, s_shard: torch.Tensor, block_h: int, mode: str,
+                 group: Optional[dist.ProcessGroup] = None, linear_fn: Optional[Callable] = None):
+        assert mode in ("column", "row")
+        self.w, self.s, self.block_h, self.mode, self.group = w_shard, s_shard, block_h, mode, group
+        self.N, self.K = int(w_shard.shape[0]), int(w_shard.shape[1])
+        self._linear = linear_fn or (lambda x: ops.w8a16_linear(x, self.w, self.s, self.N, self.K, self.block_h, 128))
+
+    def forward(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """column: x [M, K] (replicated) -> [M, N/tp].  row: x [M, K/tp] -> all-reduced [M, N]; the bias is
+        added on rank 0 only before the reduce, as vLLM does."""
+        y = self._linear(x)
+        if self.mode == "row":
+            if bias is not None and dist.get_rank(self.group) == 0:
+                y = y + bias.to(y.dtype)
+            if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+                dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+        elif bias is not None:
+            y = y + bias.to(y.dtype)
+        return y
+
+
+# ------------------------------------------------------------------------------------------------
+# expert parallelism: all-to-all dispatch / combine
+# ------------------------------------------------------------------------------------------------
+def ep_plan(topk_ids: torch.Tensor, num_experts: int, ep_size: int) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Routes of this rank's tokens grouped by destination rank (experts are partitioned contiguously).
+
+    Returns (order, send_counts, local_ids): ``order`` is a stable permutation of the valid flat route
+    indices sorted by destination rank, ``send_counts[p]`` the number of routes going to rank p and
+    ``local_ids`` the expert id local to its destination, in ``order``.  Invalid ids (< 0) are dropped."""
+    per = num_experts // ep_size
+    flat = topk_ids.reshape(-1).to(torch.int64)
+    valid = (flat >= 0) & (flat < num_experts)
+    dest = torch.where(valid, flat // per, torch.full_like(flat, ep_size))
+    order = torch.sort(dest, stable=True).indices
+    n_valid = int(valid.sum())
+    order = order[:n_valid]
+    send_counts = torch.bincount(dest[order], minlength=ep_size)[:ep_size]
+    local_ids = (flat[order] % per).to(torch.int32)
+    return order, send_counts, local_ids
+
+
+class ExpertParallelMoE:
+    """MoE layer whose experts are split over the ranks of ``group``; each rank brings its own tokens.
+
+    forward: plan -> all-to-all(rows, local expert ids) -> local experts on the received rows (each row is a
+    single-expert route, weight 1) -> all-to-all back -> weighted sum per token on the source rank."""
+
+    def __init__(self, w13: torch.Tensor, s13: torch.Tensor, w2: torch.Tensor, s2: torch.Tensor, num_experts: int,
+                 block_h: int = 128, group: Optional[dist.ProcessGroup] = None, expert_fn: Optional[Callable] = None):
+        self.w13, self.s13, self.w2, self.s2 = w13, s13, w2, s2
+        self.num_experts, self.block_h, self.group = num_experts, block_h, group
+        self.ep_size = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.local_experts = num_experts // self.ep_size
+        assert num_experts % self.ep_size == 0 and w13.shape[0] == self.local_experts
+        self._experts = expert_fn or self._engine_experts
+
+    def _engine_experts(self, rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
+        ones = torch.ones(rows.shape[0], 1, dtype=torch.float32, device=rows.device)
+        return ops.moe_forward(rows, ones, local_ids.reshape(-1, 1).contiguous(), self.w13, self.s13, self.w2, self.s2,
+                               block_h=self.block_h)
+
+    def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        M, H = x.shape
+        topk = topk_ids.shape[-1]
+        order, send_counts, local_ids = ep_plan(topk_ids, self.num_experts, self.ep_size)
+        send_rows = x.index_select(0, torch.div(order, topk, rounding_mode="floor"))
+        if self.ep_size > 1:
+            recv_counts = torch.empty_like(send_counts)
+            dist.all_to_all_single(recv_counts, send_counts, group=self.group)
+            sc, rc = send_counts.tolist(), recv_counts.tolist()      # one host synchronisation per layer
+            recv_rows = x.new_empty((sum(rc), H))
+            recv_ids = local_ids.new_empty((sum(rc),))
+            dist.all_to_all_single(recv_rows, send_rows.contiguous(), rc, sc, group=self.group)
+            dist.all_to_all_single(recv_ids, local_ids.contiguous(), rc, sc, group=self.group)
+        else:
+            sc = rc = None
+            recv_rows, recv_ids = send_rows.contiguous(), local_ids
+        y_recv = self._experts(recv_rows, recv_ids) if recv_rows.shape[0] else recv_rows
+        if self.ep_size > 1:
+            y_back = x.new_empty((send_rows.shape[0], H))
+            dist.all_to_all_single(y_back, y_recv.contiguous(), sc, rc, group=self.group)
+        else:
+            y_back = y_recv
+        # weighted combine on the source rank: route weight as FP16 like the reference (vllm_serve.py:1804)
+        w16 = topk_weights.reshape(-1)[order].to(torch.float16).float().unsqueeze(-1)
+        out = torch.zeros((M, H), dtype=torch.float32, device=x.device)
+        out.index_add_(0, torch.div(order, topk, rounding_mode="floor"), (y_back.float() * w16).to(torch.float16).float())
+        return out.to(torch.float16)
