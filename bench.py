@@ -38,6 +38,7 @@ PREFILL_M = [512, 2048, 8192]
 MOE_CFG = dict(E=128, topk=8, H=2048, I=768)
 NOMINAL_HBM_GBS = 8000.0
 NOMINAL_F16_TFLOPS = 2250.0
+GEMV_MAX_M = 4   # fp8w8a16_linear ALGO_AUTO: M <= 4 -> CUDA-core GEMV, else tcgen05 GEMM
 
 
 def algorithmic_bytes(M: int, N: int, K: int, block_h: int = 128) -> int:
@@ -171,115 +172,154 @@ def time_call(fn, reps: int, flush) -> float:
 # ------------------------------------------------------------------------------------------------
 # dense layers (decode / prefill)
 # ------------------------------------------------------------------------------------------------
-class DenseStack:
-    """`layers` copies of the four linears of one decoder layer; with world > 1 every rank holds its TP shard."""
+def graph_of(fn, stream):
+    """Warm `fn` up on `stream`, then capture it into a CUDA graph on the same stream (so the engine's
+    per-stream workspace already exists).  Decode serving replays graphs; this keeps host launch
+    overhead out of the device-time figures."""
+    with torch.cuda.stream(stream):
+        fn()
+        fn()
+    stream.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        fn()
+    return g
 
-    def __init__(self, layers: int, world: int, rank: int, device):
+
+class DenseStack:
+    """Several independent copies of each of the four linears (enough bytes per shape to defeat the 126 MB
+    L2 when the copies are cycled); with world > 1 every rank holds its TP shard of every copy."""
+
+    def __init__(self, world: int, rank: int, device, min_bytes: int = 320 << 20, max_copies: int = 12):
         from vllm_fp8_w8a16_sm70_b200 import parallel as par
         self.world, self.device = world, device
-        self.layers = []
-        for li in range(layers):
-            lin = {}
-            for si, (name, N, K, mode) in enumerate(DENSE_SHAPES):
-                q, s = synth_block_fp8(N, K, 1000 * li + si, device)
+        self.copies = {}
+        for si, (name, N, K, mode) in enumerate(DENSE_SHAPES):
+            n = max(2, min(max_copies, -(-min_bytes // (N * K // world))))
+            lst = []
+            for ci in range(n):
+                q, s = synth_block_fp8(N, K, 1000 * ci + si, device)
                 s16 = s.to(torch.float16)        # load-time cast, as process_weights_after_loading does
                 if world > 1:
                     q, s16 = (par.shard_column_parallel if mode == "column" else par.shard_row_parallel)(q, s16, world, rank)
-                lin[name] = par.TensorParallelLinear(q, s16, 128, mode)
+                lst.append(par.TensorParallelLinear(q, s16, 128, mode))
                 del s
-            self.layers.append(lin)
+            self.copies[name] = lst
         torch.cuda.empty_cache()
+
+    def lin(self, name: str, i: int):
+        lst = self.copies[name]
+        return lst[i % len(lst)]
 
     def inputs(self, M: int, seed: int = 0):
         g = torch.Generator(device=self.device).manual_seed(seed + M)
-        return {name: torch.randn(M, lin.K, generator=g, device=self.device).to(torch.float16)
-                for name, lin in self.layers[0].items()}
+        return {name: torch.randn(M, lst[0].K, generator=g, device=self.device).to(torch.float16)
+                for name, lst in self.copies.items()}
 
 
 def run_dense(args, world, rank, local, m_list, workload: str) -> dict:
     from vllm_fp8_w8a16_sm70_b200 import _cabi, ops
     device = torch.device("cuda", local)
     peaks = measured_peaks()
-    n_layers = 2 if workload == "decode" else 1
-    stack = DenseStack(n_layers, world, rank, device)
+    stack = DenseStack(world, rank, device)
     xs = {M: stack.inputs(M) for M in m_list}
     lib = _cabi.load()
+    use_graphs = (world == 1) and not args.eager
+    side = torch.cuda.Stream(device=device)
 
     def step(i: int):
-        lay = stack.layers[i % n_layers]
         for M in m_list:
             for name, _, _, _ in DENSE_SHAPES:
-                lay[name].forward(xs[M][name])
+                stack.lin(name, i).forward(xs[M][name])
 
     bytes_step = sum(algorithmic_bytes(M, N, K) for M in m_list for _, N, K, _ in DENSE_SHAPES)
     flops_step = sum(2 * M * N * K for M in m_list for _, N, K, _ in DENSE_SHAPES)
+    n_var = max(len(v) for v in stack.copies.values())      # distinct steps before a weight copy repeats
+    if use_graphs:
+        l0 = lib.fp8w8a16_launch_count()
+        graphs = [graph_of(lambda i=i: step(i), side) for i in range(n_var)]
+        launches_per_step = (lib.fp8w8a16_launch_count() - l0) // (3 * n_var)
+        run_step = lambda i: graphs[i % n_var].replay()
+    else:
+        run_step = step
     for i in range(args.warmup):
-        step(i)
+        run_step(i)
     barrier_sync(world)
     launches0 = lib.fp8w8a16_launch_count()
     with ClockSampler(local) as clk:
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for i in range(args.steps):
-            step(i)
+            run_step(i)
         b.record()
         barrier_sync(world)
         ms_total = max_over_ranks(a.elapsed_time(b), world)
-    launches = lib.fp8w8a16_launch_count() - launches0
+    launches = launches_per_step * args.steps if use_graphs else lib.fp8w8a16_launch_count() - launches0
     ms_step = ms_total / args.steps
 
     # ---- end to end through the plugin-shaped API with HOST buffers ----
-    e2e = run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, workload)
+    e2e = None if args.only else run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, workload)
 
-    # ---- per-case device times (rank-local, L2 flushed between calls) for the roofline ----
-    cases, flush = [], Flusher(device)
-    reps = 5 if workload == "decode" else 2
+    # ---- per-case device times (rank-local) for the roofline: every case cycles over its weight copies ----
+    cases = []
+    reps = 6 if workload == "decode" else 2
+    flush = Flusher(device)
     for M in m_list:
         for name, N, K, _ in DENSE_SHAPES:
-            lin = stack.layers[0][name]
-            ms = time_call(lambda: lin.forward(xs[M][name]), reps, flush)
+            lst = stack.copies[name]
+            if use_graphs:
+                g = graph_of(lambda: [lin.forward(xs[M][name]) for lin in lst], side)
+                flush()
+                torch.cuda.synchronize()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(reps):
+                    g.replay()
+                b.record()
+                b.synchronize()
+                ms = a.elapsed_time(b) / (reps * len(lst))
+                del g
+            else:
+                ms = time_call(lambda: lst[0].forward(xs[M][name]), reps, flush)
+            lin = lst[0]
             nb = algorithmic_bytes(M, lin.N, lin.K)
             cases.append({"layer": name, "M": M, "ms": round(ms, 5), "GBps": round(nb / ms / 1e6, 1),
-                          "TFLOPs": round(2 * M * lin.N * lin.K / ms / 1e9, 2), "kernel": "gemv" if M <= 4 else "gemm_tc"})
+                          "TFLOPs": round(2 * M * lin.N * lin.K / ms / 1e9, 2), "kernel": "gemv" if M <= GEMV_MAX_M else "gemm_tc"})
     st = ops.device_status(reset=True)
     if st != 0:
         raise RuntimeError(f"device status word {st:#x}: a kernel timed out on a bounded wait")
 
+    timing = "CUDA-graph replay of one step" if use_graphs else "eager launches"
     if workload == "decode":
         dom = "gemm_tc"
-        sel = [c for c in cases if c["kernel"] == dom]
+        sel = [c for c in cases if c["kernel"] == dom] or cases
         ach = sum(algorithmic_bytes(c["M"], *shape_of(stack, c["layer"])) for c in sel) / sum(c["ms"] for c in sel) / 1e6
         roof = {"bound": "hbm", "kernel": "k_gemm_tc (tcgen05 W8A16, decode tiles)", "achieved": round(ach, 1), "peak": peaks["hbm_gbs"],
                 "unit": "GB/s", "frac": round(ach / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
                 "frac_of_nominal_8TBps": round(ach / NOMINAL_HBM_GBS, 4), "traffic": None}
-        value, unit, metric = bytes_step * world_factor(world) / ms_step / 1e6, "GB/s", "w8a16_decode_gemv_hbm_GBps"
+        value, unit, metric = bytes_step / ms_step / 1e6, "GB/s", "w8a16_decode_gemv_hbm_GBps"
     else:
         ach = sum(2 * c["M"] * shape_of(stack, c["layer"])[0] * shape_of(stack, c["layer"])[1] for c in cases) / sum(c["ms"] for c in cases) / 1e9
         roof = {"bound": "tensor", "kernel": "k_gemm_tc (tcgen05 W8A16, prefill tiles)", "achieved": round(ach, 1),
                 "peak": peaks["tflops_sustained"], "unit": "TFLOP/s", "frac": round(ach / peaks["tflops_sustained"], 4),
                 "peak_source": peaks["source"] + " (sustained bf16 matmul)", "frac_of_nominal_2250": round(ach / NOMINAL_F16_TFLOPS, 4),
                 "traffic": None}
-        value, unit, metric = flops_step * world_factor(world) / ms_step / 1e9, "TFLOP/s", "w8a16_prefill_gemm_TFLOPs"
+        value, unit, metric = flops_step / ms_step / 1e9, "TFLOP/s", "w8a16_prefill_gemm_TFLOPs"
     out = {
         "metric": metric, "value": round(value, 2), "unit": unit, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic", "impl": "ours",
         "config": {"workload": f"dense {workload} sweep: qkv[7168,5120] o[5120,5120] gate_up[51200,5120] down[5120,25600], block-128 "
-                               f"E4M3 + block scales, fp16 acts, M in {m_list}", "parallelism": f"tp{world}",
-                   "l2": "weights cycled: 456 MB per layer pass x %d layer copies > 126 MB L2; per-case timings flush L2" % n_layers},
+                               f"E4M3 + block scales, fp16 acts, M in {m_list}", "parallelism": f"tp{world}", "timing": timing,
+                   "l2": "inputs larger than L2: every shape cycles over >= 320 MB of distinct weight copies (126 MB L2)"},
         "roofline": roof, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk.summary(), "cases": cases,
     }
     return out
 
 
 def shape_of(stack, name):
-    lin = stack.layers[0][name]
+    lin = stack.copies[name][0]
     return lin.N, lin.K
-
-
-def world_factor(world: int) -> int:
-    # bytes_step / flops_step are computed from the FULL layer shapes, so the whole-job figure needs no scaling
-    return 1
 
 
 def run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, workload) -> dict:
@@ -288,9 +328,10 @@ def run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, wo
     import types
     method = Fp8LinearMethod((128, 128))
     layers = []
-    for lay in stack.layers:
+    for ci in range(max(len(v) for v in stack.copies.values())):
         objs = {}
-        for name, lin in lay.items():
+        for name in stack.copies:
+            lin = stack.lin(name, ci)
             objs[name] = types.SimpleNamespace(weight=lin.w, weight_scale_inv=lin.s, weight_block_size=[128, 128],
                                                input_size_per_partition=lin.K, output_size_per_partition=lin.N, mode=lin.mode)
         layers.append(objs)
@@ -347,31 +388,46 @@ def run_moe(args, world, rank, local, m_list=(1, 8, 64, 256)) -> dict:
     layer = par.ExpertParallelMoE(w13, s13, w2, s2, E) if world > 1 else None
     lib = _cabi.load()
     results = []
+    use_graphs = (world == 1) and not args.eager
+    side = torch.cuda.Stream(device=device)
+    n_sets = 16     # distinct token batches per M, so that consecutive steps route to different experts (L2 cannot hold them)
     for M in m_list:
-        x = torch.randn(M, H, generator=g, device=device).to(torch.float16)
-        logits = torch.randn(M, E, generator=g, device=device)
+        xs = [torch.randn(M, H, generator=g, device=device).to(torch.float16) for _ in range(n_sets)]
+        lgs = [torch.randn(M, E, generator=g, device=device) for _ in range(n_sets)]
 
-        def step():
-            tw, ids = ops.moe_topk_softmax(logits, topk, True)
+        def step(j):
+            tw, ids = ops.moe_topk_softmax(lgs[j], topk, True)
             if world > 1:
-                return layer.forward(x, tw, ids)
-            return ops.moe_forward(x, tw, ids, w13, s13, w2, s2, block_h=128)
-        for _ in range(max(3, args.warmup)):
-            step()
-        barrier_sync(world)
+                return layer.forward(xs[j], tw, ids)
+            return ops.moe_forward(xs[j], tw, ids, w13, s13, w2, s2, block_h=128)
+
+        def all_sets():
+            for j in range(n_sets):
+                step(j)
         n0 = lib.fp8w8a16_launch_count()
+        if use_graphs:
+            gr = graph_of(all_sets, side)
+            run = gr.replay
+            launches_per_step = (lib.fp8w8a16_launch_count() - n0) // (3 * n_sets)
+        else:
+            run = all_sets
+            for _ in range(2):
+                run()
+            launches_per_step = (lib.fp8w8a16_launch_count() - n0) // (2 * n_sets)
+        run()
+        barrier_sync(world)
+        rounds = max(1, args.steps // n_sets)
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
-        for _ in range(args.steps):
-            step()
+        for _ in range(rounds):
+            run()
         b.record()
         barrier_sync(world)
-        ms = max_over_ranks(a.elapsed_time(b), world) / args.steps
-        tw, ids = ops.moe_topk_softmax(logits, topk, True)
-        distinct = int(torch.unique(ids).numel())
+        ms = max_over_ranks(a.elapsed_time(b), world) / (rounds * n_sets)
+        distinct = statistics.mean(int(torch.unique(ops.moe_topk_softmax(lg, topk, True)[1]).numel()) for lg in lgs)
         nbytes = distinct * (3 * I * H + 4 * (2 * I // 128 * H // 128 + H // 128 * I // 128)) + 2 * M * H * 2 + 4 * M * E
-        results.append({"M_per_gpu": M, "tok_per_s": round(world * M / ms * 1e3, 1), "ms": round(ms, 4), "distinct_experts": distinct,
-                        "GBps_active_experts": round(nbytes / ms / 1e6, 1), "launches_per_step": int((lib.fp8w8a16_launch_count() - n0) / args.steps)})
+        results.append({"M_per_gpu": M, "tok_per_s": round(world * M / ms * 1e3, 1), "ms": round(ms, 4), "distinct_experts": round(distinct, 1),
+                        "GBps_active_experts": round(nbytes / ms / 1e6, 1), "launches_per_step": int(launches_per_step)})
     st = ops.device_status(reset=True)
     if st != 0:
         raise RuntimeError(f"device status word {st:#x}")
@@ -442,6 +498,9 @@ def main() -> None:
     ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "moe"])
     ap.add_argument("--no-extras", action="store_true", help="skip the prefill / MoE side measurements")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default=None, metavar="LAYER:M", help="profiling aid: run one dense case only, e.g. gate_up:16 "
+                    "(implies --no-extras --no-cpu-baseline, skips the end-to-end leg)")
+    ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays (1 GPU)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
@@ -450,6 +509,16 @@ def main() -> None:
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device (the engine has no CPU path); use --impl reference for the CPU arm")
     world, rank, local = dist_setup(args.gpus)
+    if args.only:
+        global DENSE_SHAPES
+        name, m = args.only.split(":")
+        DENSE_SHAPES = [sh for sh in DENSE_SHAPES if sh[0] == name]
+        assert DENSE_SHAPES, f"unknown layer {name}"
+        args.no_extras = args.no_cpu_baseline = True
+        out = run_dense(args, world, rank, local, [int(m)], "decode" if int(m) <= 64 else "prefill")
+        if rank == 0:
+            print(json.dumps(out))
+        return
     if args.workload == "decode":
         out = run_dense(args, world, rank, local, DECODE_M, "decode")
     elif args.workload == "prefill":

@@ -73,7 +73,7 @@ def test_linear_method_load_time_rules(lib):
     assert layer.weight.dtype == torch.float8_e4m3fn and tuple(layer.weight.shape) == (256, 384)
     with pytest.raises(NotImplementedError):
         Fp8LinearMethod(None).process_weights_after_loading(layer)
-    layer.weight_scale_inv = torch.full((2, 3), 300.0)
+    layer.weight_scale_inv = torch.full((2, 3), 1.0e6)   # overflows FP16
     with pytest.raises(RuntimeError, match="scale"):
         Fp8LinearMethod((128, 128)).process_weights_after_loading(layer)
     # compressed-tensors channel: [N,1] -> [N, Kb] block_h = 1 grid (compressed_tensors_v100.py:488-492)

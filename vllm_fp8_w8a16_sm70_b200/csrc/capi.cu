@@ -63,49 +63,10 @@ namespace {
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
-// Number of K splits for `tiles` output tiles of `total_kb` K blocks each: the smallest split count
-// that fills at least 85 % of the last wave of SMs, leaving every split at least two K blocks.
-int pick_splits(int tiles, int total_kb) {
-    const int sms = sm_count();
-    if (tiles >= sms || total_kb < 4) return 1;
-    int max_s = total_kb / 2;
-    if (max_s > 16) max_s = 16;
-    int best = 1;
-    double best_eff = 0.0;
-    for (int s = 1; s <= max_s; ++s) {
-        const int units = tiles * s;
-        const int waves = (units + sms - 1) / sms;
-        const double eff = (double)units / ((double)sms * waves);
-        if (eff > best_eff + 1e-9) {
-            best_eff = eff;
-            best = s;
-        }
-        if (eff >= 0.85) return s;
-    }
-    return best;
-}
-
-struct SplitPlan {
-    int splits;
-    int kb_per_split;
-};
-
-SplitPlan plan_splits(int tiles_for_heuristic, int tiles_upper_bound, int K, int bk) {
-    const int total_kb = (K + bk - 1) / bk;
-    int s = pick_splits(tiles_for_heuristic, total_kb);
-    if ((size_t)tiles_upper_bound * sizeof(unsigned int) > kTicketBytes) s = 1;
-    SplitPlan sp;
-    sp.kb_per_split = (total_kb + s - 1) / s;
-    sp.splits = (total_kb + sp.kb_per_split - 1) / sp.kb_per_split;
-    return sp;
-}
-
 size_t tc_dense_workspace_bytes(int M, int N, int K) {
-    const int bt = tc_pick_bt(M), bk = tc_block_k(bt, false);
-    const int tiles = ((N + 127) / 128) * ((M + bt - 1) / bt);
-    const SplitPlan sp = plan_splits(tiles, tiles, K, bk);
-    const size_t partial = sp.splits > 1 ? (size_t)tiles * sp.splits * bt * 128 * sizeof(float) : 0;
-    return kTicketBytes + align_up(partial, 256);
+    (void)N;
+    (void)K;
+    return tc_workspace_bytes(tc_pick_bt(M), false);
 }
 
 int check_common(const void* x, const void* w, const void* scales, const void* out, int M, int N, int K, int block_h,
@@ -126,8 +87,10 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
               int block_h, void* workspace, size_t workspace_bytes, cudaStream_t st) {
     const int bt = tc_pick_bt(M), bk = tc_block_k(bt, false);
     const int token_tiles = (M + bt - 1) / bt;
-    const int tiles = ((N + 127) / 128) * token_tiles;
-    const SplitPlan sp = plan_splits(tiles, tiles, K, bk);
+    const int64_t tiles = (int64_t)((N + 127) / 128) * token_tiles;
+    const size_t need = tc_workspace_bytes(bt, false);
+    W8A16_REQUIRE(workspace != nullptr && workspace_bytes >= need, FP8W8A16_ERR_WORKSPACE,
+                  "linear: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
     TcLaunch L;
     memset(&L, 0, sizeof(L));
     L.p.M = M;
@@ -143,19 +106,15 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
     L.p.num_experts = 1;
     L.p.out = out;
     L.p.ldo = N;
-    L.p.splits = sp.splits;
-    L.p.kblocks_per_split = sp.kb_per_split;
-    if (sp.splits > 1) {
-        const size_t need = kTicketBytes + (size_t)tiles * sp.splits * bt * 128 * sizeof(float);
-        W8A16_REQUIRE(workspace != nullptr && workspace_bytes >= need, FP8W8A16_ERR_WORKSPACE,
-                      "linear: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
-        L.p.tickets = reinterpret_cast<unsigned int*>(workspace);
-        L.p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kTicketBytes);
-    }
+    L.p.n_token_tiles = token_tiles;
+    L.p.no_split = tiles > (int64_t)tc_max_tiles_with_tickets() ? 1 : 0;
+    L.p.tickets = reinterpret_cast<unsigned int*>(workspace);
+    L.p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kTicketBytes);
     L.w = w;
     L.x = x;
     L.w_total_rows = N;
-    L.token_tiles = token_tiles;
+    L.max_units = tiles * ((K + bk - 1) / bk);
+    W8A16_REQUIRE(L.max_units < (1ll << 31), FP8W8A16_ERR_UNSUPPORTED, "linear: problem too large for 32-bit work indices");
     return tc_launch(L, bt, false, st);
 }
 
@@ -168,29 +127,16 @@ int token_tile_for(int R, int E) {
 
 int token_tiles_upper_bound(int R, int E, int bt) { return (R < E ? R : E) + R / bt; }
 
-struct GroupedPlan {
-    int n_slabs, tiles_ub, bk;
-    SplitPlan sp;
-    size_t partial_bytes;
-};
-
-GroupedPlan plan_grouped(int R, int E, int N, int K, int paired, int bt) {
-    GroupedPlan g;
-    g.bk = tc_block_k(bt, paired != 0);
-    g.n_slabs = (N + 127) / 128;
-    g.tiles_ub = token_tiles_upper_bound(R, E, bt) * g.n_slabs;
-    const int active = (R < E ? R : E) * g.n_slabs;  // tiles that certainly stream distinct weights
-    g.sp = plan_splits(active > 0 ? active : 1, g.tiles_ub, K, g.bk);
-    g.partial_bytes = g.sp.splits > 1 ? (size_t)g.tiles_ub * g.sp.splits * (paired ? 2 : 1) * bt * 128 * sizeof(float) : 0;
-    return g;
-}
-
 int grouped_gemm(const __half* x_sorted, const uint8_t* w, const void* scales, int scale_dtype, __half* out,
                  const float* row_weight, const int* offsets, const int* tile_offsets, int R, int E, int N, int K,
                  int block_h, int paired, int bt, void* workspace, size_t workspace_bytes, cudaStream_t st) {
     if (R == 0 || N == 0) return 0;
-    const GroupedPlan g = plan_grouped(R, E, N, K, paired, bt);
+    const int bk = tc_block_k(bt, paired != 0);
     const int rows_w = paired ? 2 * N : N;
+    const int64_t tiles_ub = (int64_t)token_tiles_upper_bound(R, E, bt) * ((N + 127) / 128);
+    const size_t need = tc_workspace_bytes(bt, paired != 0);
+    W8A16_REQUIRE(workspace != nullptr && workspace_bytes >= need, FP8W8A16_ERR_WORKSPACE,
+                  "moe_grouped_gemm: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
     TcLaunch L;
     memset(&L, 0, sizeof(L));
     L.p.M = R;
@@ -209,19 +155,15 @@ int grouped_gemm(const __half* x_sorted, const uint8_t* w, const void* scales, i
     L.p.out = out;
     L.p.ldo = N;
     L.p.row_weight = row_weight;
-    L.p.splits = g.sp.splits;
-    L.p.kblocks_per_split = g.sp.kb_per_split;
-    if (g.sp.splits > 1) {
-        const size_t need = kTicketBytes + g.partial_bytes;
-        W8A16_REQUIRE(workspace != nullptr && workspace_bytes >= need, FP8W8A16_ERR_WORKSPACE,
-                      "moe_grouped_gemm: workspace too small (%zu < %zu bytes)", workspace_bytes, need);
-        L.p.tickets = reinterpret_cast<unsigned int*>(workspace);
-        L.p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kTicketBytes);
-    }
+    L.p.n_token_tiles = 0;
+    L.p.no_split = tiles_ub > (int64_t)tc_max_tiles_with_tickets() ? 1 : 0;
+    L.p.tickets = reinterpret_cast<unsigned int*>(workspace);
+    L.p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kTicketBytes);
     L.w = w;
     L.x = x_sorted;
     L.w_total_rows = (int64_t)E * rows_w;
-    L.token_tiles = token_tiles_upper_bound(R, E, bt);
+    L.max_units = tiles_ub * ((K + bk - 1) / bk);
+    W8A16_REQUIRE(L.max_units < (1ll << 31), FP8W8A16_ERR_UNSUPPORTED, "moe_grouped_gemm: problem too large for 32-bit work indices");
     return tc_launch(L, bt, paired != 0, st);
 }
 
@@ -239,11 +181,9 @@ MoeLayout moe_layout(int M, int topk, int E, int H, int I) {
     size_t o = kTicketBytes;  // the grouped GEMMs' ticket header sits at the very start
     // the GEMM scratch (tickets + partials) must be one contiguous block: header first, partials
     // right after it; the bookkeeping arrays follow the partials.
-    const GroupedPlan g13 = plan_grouped(R > 0 ? R : 1, E, I, H, 1, L.bt);
-    const GroupedPlan g2 = plan_grouped(R > 0 ? R : 1, E, H, I, 0, L.bt);
-    const size_t partial = g13.partial_bytes > g2.partial_bytes ? g13.partial_bytes : g2.partial_bytes;
+    const size_t a13 = tc_workspace_bytes(L.bt, true), a2 = tc_workspace_bytes(L.bt, false);
     L.gemm_ws = 0;
-    L.gemm_ws_bytes = kTicketBytes + align_up(partial, 256);
+    L.gemm_ws_bytes = align_up(a13 > a2 ? a13 : a2, 256);
     o = L.gemm_ws_bytes;
     auto take = [&o](size_t bytes) {
         const size_t at = o;
@@ -358,9 +298,11 @@ int fp8w8a16_moe_align(const void* topk_ids, int ids_are_i64, int R, const int32
 }
 
 size_t fp8w8a16_moe_grouped_gemm_workspace_bytes(int R, int num_local_experts, int N, int K, int paired, int token_tile) {
-    if (R <= 0 || num_local_experts <= 0 || N <= 0 || K <= 0) return kTicketBytes;
-    const GroupedPlan g = plan_grouped(R, num_local_experts, N, K, paired, token_tile);
-    return kTicketBytes + align_up(g.partial_bytes, 256);
+    (void)R;
+    (void)num_local_experts;
+    (void)N;
+    (void)K;
+    return tc_workspace_bytes(token_tile, paired != 0);
 }
 
 int fp8w8a16_moe_grouped_gemm(const uint16_t* x_sorted, const uint8_t* w, const void* scales, int scale_dtype,

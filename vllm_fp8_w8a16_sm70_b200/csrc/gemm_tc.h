@@ -28,11 +28,11 @@ struct TcParams {
     __half* out;                 // out[row * ldo + n]
     int64_t ldo;
     const float* row_weight;     // optional per-row multiplier (route weight), applied as FP16
-    // split-K
-    float* partial;              // fp32 scratch: [tiles][splits][(1|2)][BT][128]
-    unsigned int* tickets;       // one counter per tile, zero on entry and on exit
-    int splits;
-    int kblocks_per_split;
+    // persistent stream-K work split
+    int n_token_tiles;           // dense: ceil(M / BT); grouped: read from tile_offsets[E] on the device
+    int no_split;                // 1: every CTA takes whole tiles only (no partial tiles, no tickets)
+    float* partial;              // fp32 scratch: [gridDim.x][2][(1|2)][BT][128]
+    unsigned int* tickets;       // one counter per output tile, zero on entry and on exit
 };
 
 struct TcLaunch {
@@ -40,11 +40,16 @@ struct TcLaunch {
     const uint8_t* w;
     const __half* x;
     int64_t w_total_rows;        // num_experts * w_rows_per_expert
-    int token_tiles;             // gridDim.y (dense: ceil(M / BT); grouped: an upper bound)
+    int64_t max_units;           // upper bound on (output tiles x K blocks): caps the grid
 };
 
 int tc_pick_bt(int rows);
 int tc_block_k(int bt, bool paired);
+int tc_ctas_per_sm(int bt, bool paired);
+// CTAs the persistent launch uses on the current device, and the scratch it needs (ticket header included).
+int tc_grid(int bt, bool paired);
+size_t tc_workspace_bytes(int bt, bool paired);
+size_t tc_max_tiles_with_tickets();
 int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st);
 int tc_read_status(int* out, int reset);
 

@@ -3,8 +3,8 @@
 // HBM-bound on the FP8 weight stream.  One warp owns R = 4 consecutive weight rows and one K range;
 // a lane reads 16 weight bytes per row per step (a warp covers 512 contiguous bytes of each row with
 // one 16-byte load per lane), so 4 independent 16-byte loads per lane are in flight per step and the
-// activations are fetched once per step for all 4 rows.  Dequant happens in registers, products are
-// accumulated in fp32 per 16-element run and multiplied by the block (or channel) scale once per
+// activations are fetched once per step for all 4 rows.  Dequant happens in registers (hardware
+// cvt.rn.f16x2.e4m3x2), products are accumulated in fp32 (fma.rn.f32.f16) per 16-element run and multiplied by the block (or channel) scale once per
 // run, the lanes are reduced with warp shuffles.  K is split across blockIdx.y; partial sums go to
 // an fp32 workspace and the LAST CTA to arrive for a row block (ticket counter) adds them in fixed
 // split order, so the result does not depend on scheduling.
@@ -23,26 +23,20 @@ constexpr int kThreads = kWarps * 32;
 constexpr int kRowsPerCta = kRows * kWarps;
 constexpr int kStep = 512;             // K elements one warp covers per step
 
-// 16 E4M3 bytes (uint4) times 16 activations -> fp32 dot product, weights taken as
-// (magnitude * 2^-8) with sign; the caller folds 2^8 into the scale.
+// 16 E4M3 bytes (uint4) times 16 FP16 activations (8 packed pairs per token) -> fp32 dot products.
+// Weights are converted with the hardware cvt (exact) and multiplied in fma.rn.f32.f16; the block
+// scale is applied by the caller once per 16-element run.
 template <int M>
-__device__ __forceinline__ void dot16(const uint4& q, const float (&xf)[M][16], float (&part)[M]) {
+__device__ __forceinline__ void dot16(const uint4& q, const uint32_t (&xh)[M][8], float (&part)[M]) {
     const uint32_t words[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
     for (int t = 0; t < 4; ++t) {
-        uint32_t m01, g01, m23, g23;
-        e4m3x2_split(words[t], 0x1404u, m01, g01);
-        e4m3x2_split(words[t], 0x3424u, m23, g23);
-        m01 ^= g01;
-        m23 ^= g23;
-        const float2 w01 = __half22float2(*reinterpret_cast<__half2*>(&m01));
-        const float2 w23 = __half22float2(*reinterpret_cast<__half2*>(&m23));
+        uint32_t w01, w23;
+        e4m3x4_cvt(words[t], w01, w23);
 #pragma unroll
         for (int m = 0; m < M; ++m) {
-            part[m] = fmaf(w01.x, xf[m][4 * t + 0], part[m]);
-            part[m] = fmaf(w01.y, xf[m][4 * t + 1], part[m]);
-            part[m] = fmaf(w23.x, xf[m][4 * t + 2], part[m]);
-            part[m] = fmaf(w23.y, xf[m][4 * t + 3], part[m]);
+            fma2_f32_f16(part[m], w01, xh[m][2 * t]);
+            fma2_f32_f16(part[m], w23, xh[m][2 * t + 1]);
         }
     }
 }
@@ -79,36 +73,31 @@ k_gemv(const __half* __restrict__ x, const uint8_t* __restrict__ w, const void* 
             uint4 q[kRows];
 #pragma unroll
             for (int r = 0; r < kRows; ++r) q[r] = __ldcs(reinterpret_cast<const uint4*>(wrow[r] + k));
-            float xf[M][16];
+            uint32_t xh[M][8];
 #pragma unroll
             for (int m = 0; m < M; ++m) {
                 const uint4 a0 = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)m * K + k));
                 const uint4 a1 = __ldg(reinterpret_cast<const uint4*>(x + (int64_t)m * K + k) + 1);
-                const uint32_t aw[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
-                    xf[m][2 * i] = f.x;
-                    xf[m][2 * i + 1] = f.y;
-                }
+                xh[m][0] = a0.x; xh[m][1] = a0.y; xh[m][2] = a0.z; xh[m][3] = a0.w;
+                xh[m][4] = a1.x; xh[m][5] = a1.y; xh[m][6] = a1.z; xh[m][7] = a1.w;
             }
             const int kb = k >> 7;
             float s[kRows];
             if (one_scale) {
-                const float s0 = __half2float(load_scale_h(scales, srow[0] + kb, scale_dtype)) * 256.f;
+                const float s0 = __half2float(load_scale_h(scales, srow[0] + kb, scale_dtype));
 #pragma unroll
                 for (int r = 0; r < kRows; ++r) s[r] = s0;
             } else {
 #pragma unroll
                 for (int r = 0; r < kRows; ++r)
-                    s[r] = __half2float(load_scale_h(scales, srow[r] + kb, scale_dtype)) * 256.f;
+                    s[r] = __half2float(load_scale_h(scales, srow[r] + kb, scale_dtype));
             }
 #pragma unroll
             for (int r = 0; r < kRows; ++r) {
                 float part[M];
 #pragma unroll
                 for (int m = 0; m < M; ++m) part[m] = 0.f;
-                dot16<M>(q[r], xf, part);
+                dot16<M>(q[r], xh, part);
 #pragma unroll
                 for (int m = 0; m < M; ++m) acc[r][m] = fmaf(s[r], part[m], acc[r][m]);
             }
