@@ -80,6 +80,20 @@ int fp8w8a16_linear(const uint16_t* x, const uint8_t* w, const void* scales, int
                     int N, int K, int block_h, int block_w, int algo, void* workspace, size_t workspace_bytes,
                     void* stream);
 
+/* Same result as fp8w8a16_linear with FP8W8A16_ALGO_GEMV, for callers that cannot allocate device
+ * memory and so cannot provide a workspace (a worker whose memory was all handed out at start-up,
+ * code under a no-allocation policy, a plugin that only ever receives input and output buffers).  It has no
+ * counterpart in the reference, whose ops allocate inside every call.  The scratch the split-K GEMV
+ * needs lives in a fixed array of FP8W8A16_NOALLOC_SCRATCH_BYTES inside the library image, resident
+ * on every GPU that loads the library until the process exits; the call itself allocates nothing.
+ * Shapes that need more scratch are rejected with FP8W8A16_ERR_WORKSPACE (use fp8w8a16_linear).
+ * The first call on a device looks the array's address up (cudaGetSymbolAddress) and should be made
+ * before any stream capture starts.  All calls on a device share the array: calls that overlap on the
+ * GPU race on it; calls ordered on one stream (or by events) are safe. */
+#define FP8W8A16_NOALLOC_SCRATCH_BYTES (768u << 10)
+int fp8w8a16_linear_noalloc(const uint16_t* x, const uint8_t* w, const void* scales, int scale_dtype, uint16_t* out,
+                            int M, int N, int K, int block_h, int block_w, void* stream);
+
 /* Router: logits [M,E] -> topk_ids int32 [M,topk] (descending, ties to the lowest expert id),
  * topk_weights fp32 [M,topk] = softmax probabilities of the picks (renormalize != 0: divided by
  * their sum).  Stands in for vLLM's fused_topk, whose output the reference's MoE apply consumes

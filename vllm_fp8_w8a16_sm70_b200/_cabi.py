@@ -30,6 +30,7 @@ PROTOTYPES = {
     "fp8w8a16_linear_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "fp8w8a16_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_void_p, c_size_t, c_void_p]),
+    "fp8w8a16_linear_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "fp8w8a16_moe_topk_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "fp8w8a16_moe_align": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p]),

@@ -166,6 +166,28 @@ def w8a16_linear(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, N: int,
     return out
 
 
+NOALLOC_SCRATCH_BYTES = 768 << 10
+
+
+def w8a16_linear_noalloc(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, out: torch.Tensor, N: int, K: int,
+                         block_h: int = 128, block_w: int = 128) -> torch.Tensor:
+    """Decode GEMV into a caller-provided ``out`` without allocating anything, for callers that may not
+    touch the allocator (fixed memory pools, no-allocation policies).  Scratch is a 768 KiB array inside the library;
+    larger shapes raise.  Calls that overlap on the GPU share that array and race; order them."""
+    w = _as_u8(w)
+    dev = _require_cuda(x, w, scales, out)
+    if x.dtype != torch.float16 or out.dtype != torch.float16:
+        raise RuntimeError("x and out must be float16")
+    M = x.shape[0]
+    if tuple(out.shape) != (M, N) or x.shape[1] != K or w.numel() != N * K:
+        raise RuntimeError("shape mismatch")
+    with _dev_guard(dev):
+        _cabi.check(_cabi.load().fp8w8a16_linear_noalloc(x.data_ptr(), w.data_ptr(), scales.data_ptr(), _scale_dtype(scales),
+                                                          out.data_ptr(), M, N, K, block_h, block_w, _stream(dev)),
+                    "fp8w8a16_linear_noalloc")
+    return out
+
+
 # ------------------------------------------------------------------------------------------------
 # MoE
 # ------------------------------------------------------------------------------------------------
