@@ -112,7 +112,7 @@ int fp8w8a16_moe_align(const void* topk_ids, int ids_are_i64, int R, const int32
                        int num_local_experts, int token_tile, int32_t* counts, int32_t* offsets, int32_t* tile_offsets,
                        int32_t* sorted_route, int32_t* inv_pos, void* stream);
 
-/* Token tile (16..256) the grouped GEMM uses for R routed rows over E experts. */
+/* Token tile (16..128) the grouped GEMM uses for R routed rows over E experts. */
 int fp8w8a16_moe_token_tile(int R, int num_local_experts);
 
 /* Grouped expert GEMM over expert-sorted rows:

@@ -46,7 +46,7 @@ def test_validation_returns_codes_without_a_gpu(lib):
     assert lib.fp8w8a16_linear(None, None, None, 0, None, 0, 128, 128, 128, 128, 0, None, 0, None) == 0
     assert lib.fp8w8a16_e4m3_to_fp16(None, None, 0, None) == 0
     assert lib.fp8w8a16_linear_workspace_bytes(1, 5120, 5120) >= 65536
-    assert lib.fp8w8a16_moe_token_tile(8, 128) == 16 and lib.fp8w8a16_moe_token_tile(16384, 128) == 256
+    assert lib.fp8w8a16_moe_token_tile(8, 128) == 16 and lib.fp8w8a16_moe_token_tile(16384, 128) == 128
 
 
 def test_ops_refuse_cpu_tensors(lib):

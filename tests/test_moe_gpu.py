@@ -30,7 +30,7 @@ def test_topk_softmax_indices_bit_exact(ops, M, E, k, dtype, renorm):
     assert torch.allclose(w_g.cpu(), w_o, rtol=2e-5, atol=1e-7)
 
 
-@pytest.mark.parametrize("R,E,bt", [(8, 128, 16), (2048, 128, 32), (0, 8, 16), (1, 1, 16), (777, 5, 64), (16384, 128, 256), (40000, 16, 128)])
+@pytest.mark.parametrize("R,E,bt", [(8, 128, 16), (2048, 128, 32), (0, 8, 16), (1, 1, 16), (777, 5, 64), (16384, 128, 128), (40000, 16, 128)])
 def test_align_matches_oracle(ops, R, E, bt):
     g = torch.Generator().manual_seed(R + E)
     ids = torch.randint(-1, E + 2, (R,), generator=g, dtype=torch.int64) if R else torch.zeros(0, dtype=torch.int64)

@@ -107,7 +107,8 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
     L.p.out = out;
     L.p.ldo = N;
     L.p.n_token_tiles = token_tiles;
-    L.p.no_split = tiles > (int64_t)tc_max_tiles_with_tickets() ? 1 : 0;
+    // many tiles per CTA: whole tiles cost < 12 % in the last wave and need no partial-tile traffic
+    L.p.no_split = (tiles > (int64_t)tc_max_tiles_with_tickets() || tiles >= 8ll * tc_grid(bt, false)) ? 1 : 0;
     L.p.tickets = reinterpret_cast<unsigned int*>(workspace);
     L.p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kTicketBytes);
     L.w = w;
@@ -121,7 +122,7 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
 int token_tile_for(int R, int E) {
     const int avg = (R + E - 1) / E;
     int bt = tc_pick_bt(2 * avg);
-    if (bt > 256) bt = 256;
+    if (bt > 128) bt = 128;  // the paired gate/up kernel keeps two accumulators in TMEM: 128 tokens at most
     return bt;
 }
 

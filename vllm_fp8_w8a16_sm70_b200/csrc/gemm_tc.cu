@@ -125,6 +125,23 @@ __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint6
         ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// Same with the A operand read from tensor memory (128 lanes x 8 columns per K = 16 step).
+__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Eight 32-bit registers (16 FP16 values, K ascending, even K in the low half) -> eight consecutive
+// TMEM columns of this thread's lane.
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -167,27 +184,44 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // ---- compile-time configuration ------------------------------------------------------------------
+// TMEM columns of one CTA: [0, kAccCols) fp32 accumulators (BT per weight tile), then kNA stages of
+// the dequantised FP16 A operand (BK / 2 columns per weight tile: two K elements per 32-bit cell).
 template <int BT, int BK, bool PAIRED>
 struct TcCfg {
     static constexpr int kWT = PAIRED ? 2 : 1;                 // weight tiles per stage (gate + up)
-    static constexpr int kSlabs = BK / 64;                     // 64-element (128-byte) K slabs per stage
+    static constexpr int kSlabs = BK / 64;                     // 64-element (128-byte) K slabs of the activation tile
     static constexpr int kRawBytes = 128 * BK * kWT;           // FP8 tile(s)
     static constexpr int kXBytes = BT * BK * 2;                // FP16 activation tile
-    static constexpr int kABytes = 128 * BK * 2 * kWT;         // dequantised FP16 tile(s)
-    // Decode tiles (<= 64 tokens, single weight tile) are sized so that TWO CTAs share an SM: one
-    // CTA's prologue / epilogue hides behind the other's main loop and 16 warps do the dequant.
-    static constexpr int kCtasPerSm = (!PAIRED && BT <= 64) ? 2 : 1;
-    static constexpr int kNA = (kCtasPerSm == 1 && kABytes <= 16384) ? 3 : 2;   // dequantised-operand stages
-    static constexpr int kBudget = (kCtasPerSm == 2 ? 112 : 225) * 1024 - 2048; // dynamic shared memory we allow ourselves
-    static constexpr int kNSraw = (kBudget - kNA * kABytes) / (kRawBytes + kXBytes);
-    static constexpr int kNS = kNSraw > 8 ? 8 : kNSraw;        // TMA ring stages
+    static constexpr int kACols = (BK / 2) * kWT;              // TMEM columns of one dequantised stage
     static constexpr int kAccCols = BT * kWT;
-    static constexpr int kTmemCols = kAccCols <= 32 ? 32 : kAccCols <= 64 ? 64 : kAccCols <= 128 ? 128 : kAccCols <= 256 ? 256 : 512;
+    // Small token tiles are sized so that TWO CTAs share an SM (half of shared memory and of TMEM
+    // each): one CTA's prologue / epilogue hides behind the other's main loop, 16 warps dequantise.
+    static constexpr int kCtasPerSm = (BT * kWT <= 64) ? 2 : 1;
+    static constexpr int kTmemBudget = 512 / kCtasPerSm;
+    static constexpr int kNAraw = (kTmemBudget - kAccCols) / kACols;
+    static constexpr int kNA = kNAraw > 4 ? 4 : kNAraw;        // dequantised-operand stages (TMEM)
+    static constexpr int kUsedCols = kAccCols + kNA * kACols;
+    static constexpr int kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128 : kUsedCols <= 256 ? 256 : 512;
+    static constexpr int kBudget = (kCtasPerSm == 2 ? 112 : 225) * 1024 - 2048;  // dynamic shared memory we allow ourselves
+    static constexpr int kNSraw = kBudget / (kRawBytes + kXBytes);
+    static constexpr int kNS = kNSraw > 8 ? 8 : kNSraw;        // TMA ring stages
     static constexpr int kNumBars = 4 * kNS + 2 * kNA + 1;
-    static constexpr int kSmemBytes = 1024 + kNS * (kRawBytes + kXBytes) + kNA * kABytes + kNumBars * 8 + 64;
+    static constexpr int kSmemBytes = 1024 + kNS * (kRawBytes + kXBytes) + kNumBars * 8 + 64;
     static_assert(kNS >= 2, "not enough shared memory for a 2-stage TMA ring");
-    static_assert(kAccCols <= 512, "accumulators exceed TMEM");
+    static_assert(kNA >= 2, "not enough TMEM for two dequantised stages");
     static_assert(kTmemCols * kCtasPerSm <= 512, "co-resident CTAs exceed TMEM");
+};
+
+// ring position: stage index and the parity of the current pass over the ring
+struct Ring {
+    int stage = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance(int n) {
+        if (++stage == n) {
+            stage = 0;
+            phase ^= 1u;
+        }
+    }
 };
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
@@ -280,8 +314,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     const uint32_t s_base = (dyn_base + 1023u) & ~1023u;
     const uint32_t s_raw = s_base;
     const uint32_t s_x = s_raw + kNS * C::kRawBytes;
-    const uint32_t s_a = s_x + kNS * C::kXBytes;
-    const uint32_t s_bar = s_a + kNA * C::kABytes;
+    const uint32_t s_bar = s_x + kNS * C::kXBytes;
     const uint32_t bar_full_raw = s_bar, bar_empty_raw = s_bar + 8 * kNS, bar_full_x = s_bar + 16 * kNS,
                    bar_empty_x = s_bar + 24 * kNS, bar_full_a = s_bar + 32 * kNS, bar_empty_a = bar_full_a + 8 * kNA,
                    bar_acc = bar_empty_a + 8 * kNA;
@@ -305,7 +338,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         }
         mbar_init(bar_acc, 1);
         *s_dead = 0;
-        *s_ticket = 0;
+        s_ticket[0] = 0;
+        s_ticket[1] = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(smem_u32(s_tmem), C::kTmemCols);
@@ -313,20 +347,21 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
+    const uint32_t tmem_a0 = tmem_base + C::kAccCols;  // first column of the dequantised-operand stages
 
     if (warp == 0) {
         // ================= TMA producer =================
         if (lane == 0) {
-            int it = 0;  // K blocks issued so far by this CTA (ring position)
+            Ring ring;
             bool ok = true;
             for (int u = u_begin; u < u_end && ok;) {
                 Seg sg;
                 get_seg<BT>(p, u, u_end, total_kb, n_tt, units_per_cta, sg);
                 const int w_row = sg.expert * p.w_rows_per_expert + sg.slab * 128;
-                for (int j = 0; j < sg.nkb; ++j, ++it) {
-                    const int s = it % kNS;
-                    const uint32_t ph = (uint32_t)(it / kNS) & 1u;
-                    ok = mbar_wait(bar_empty_raw + 8 * s, ph ^ 1u, s_dead, 1) && mbar_wait(bar_empty_x + 8 * s, ph ^ 1u, s_dead, 2);
+                for (int j = 0; j < sg.nkb; ++j) {
+                    const int s = ring.stage;
+                    ok = mbar_wait(bar_empty_raw + 8 * s, ring.phase ^ 1u, s_dead, 1) &&
+                         mbar_wait(bar_empty_x + 8 * s, ring.phase ^ 1u, s_dead, 2);
                     if (!ok) break;
                     const int k0 = (sg.kb0 + j) * BK;
                     mbar_arrive_expect_tx(bar_full_raw + 8 * s, C::kRawBytes);
@@ -336,6 +371,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #pragma unroll
                     for (int sl = 0; sl < C::kSlabs; ++sl)
                         tma_load_2d(s_x + s * C::kXBytes + sl * (BT * 128), &map_x, bar_full_x + 8 * s, k0 + sl * 64, sg.row_begin);
+                    ring.advance(kNS);
                 }
                 u += sg.nkb;
             }
@@ -344,31 +380,33 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         // ================= MMA issuer =================
         if (lane == 0) {
             constexpr uint32_t idesc = make_idesc_f16(BT);
-            int it = 0;
+            Ring rx, ra;
             bool ok = true;
             for (int u = u_begin; u < u_end && ok;) {
                 const int tile = u / total_kb;
                 const int nkb = min(total_kb - (u - tile * total_kb), u_end - u);
-                for (int j = 0; j < nkb; ++j, ++it) {
-                    const int sa = it % kNA, sx = it % kNS;
-                    ok = mbar_wait(bar_full_a + 8 * sa, (uint32_t)(it / kNA) & 1u, s_dead, 4) &&
-                         mbar_wait(bar_full_x + 8 * sx, (uint32_t)(it / kNS) & 1u, s_dead, 8);
+                for (int j = 0; j < nkb; ++j) {
+                    ok = mbar_wait(bar_full_a + 8 * ra.stage, ra.phase, s_dead, 4) &&
+                         mbar_wait(bar_full_x + 8 * rx.stage, rx.phase, s_dead, 8);
                     if (!ok) break;
                     tc_fence_after();
-                    const uint32_t a_st = s_a + sa * C::kABytes, x_st = s_x + sx * C::kXBytes;
+                    const uint32_t a_col = tmem_a0 + ra.stage * C::kACols;
+                    const uint32_t x_st = s_x + rx.stage * C::kXBytes;
 #pragma unroll
                     for (int sl = 0; sl < C::kSlabs; ++sl) {
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
                             const uint32_t acc = (j > 0 || sl > 0 || kk > 0) ? 1u : 0u;  // first MMA of a segment overwrites
                             const uint64_t db = make_desc_sw128(x_st + sl * (BT * 128) + kk * 32);
-                            umma_f16(tmem_base, make_desc_sw128(a_st + sl * 16384 + kk * 32), db, idesc, acc);
-                            if (PAIRED)
-                                umma_f16(tmem_base + BT, make_desc_sw128(a_st + (C::kSlabs + sl) * 16384 + kk * 32), db, idesc, acc);
+                            const uint32_t a_k = a_col + (sl * 4 + kk) * 8;           // 16 K elements = 8 columns
+                            umma_f16_ts(tmem_base, a_k, db, idesc, acc);
+                            if (PAIRED) umma_f16_ts(tmem_base + BT, a_k + BK / 2, db, idesc, acc);
                         }
                     }
-                    umma_commit(bar_empty_a + 8 * sa);
-                    umma_commit(bar_empty_x + 8 * sx);
+                    umma_commit(bar_empty_a + 8 * ra.stage);
+                    umma_commit(bar_empty_x + 8 * rx.stage);
+                    ra.advance(kNA);
+                    rx.advance(kNS);
                 }
                 if (ok) umma_commit(bar_acc);  // accumulators of this segment are complete
                 u += nkb;
@@ -376,20 +414,22 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         }
     } else {
         // ================= dequant warps; after each segment, the epilogue =================
+        // A warp may touch only the TMEM lanes of its quarter (warp % 4), so the weight row a thread
+        // converts is 32 * (warp % 4) + lane; the two warps of a quarter split the K range of a stage.
         const int td = threadIdx.x - 64;
-        const int r = td & 127;   // weight row inside the slab == TMEM lane
-        const int hk = td >> 7;   // which half of the K range of the stage
-        constexpr int kCPT = BK / 32;  // 16-byte chunks per thread per weight tile
+        const int q4 = warp & 3;
+        const int r = q4 * 32 + lane;           // weight row inside the slab == TMEM lane
+        const int hk = (warp - 2) >> 2;         // which half of the stage's K range (and of the epilogue's columns)
+        constexpr int kCPT = BK / 32;           // 16-byte chunks per thread per weight tile
         const uint32_t r7 = (uint32_t)(r & 7);
-        const uint32_t a_row_off = (uint32_t)((r >> 3) * 1024 + (r & 7) * 128);
-        const int q4 = warp & 3;              // TMEM lane quarter this warp may read
-        const int ch = (warp - 2) >> 2;       // column half handled in the epilogue
-        const int n_local = q4 * 32 + lane;
+        const int n_local = r;
         const uint32_t t_lane = tmem_base + ((uint32_t)(q4 * 32) << 16);
+        const uint32_t t_lane_a = t_lane + C::kAccCols;
         constexpr int kColsPerWarp = BT / 2;
         constexpr int kTileFloats = C::kWT * BT * 128;
 
-        int it = 0, seg_idx = 0;
+        Ring rr, ra;   // raw-tile ring (shared memory) and dequantised-operand ring (TMEM)
+        int seg_idx = 0;
         bool ok = true;
         for (int u = u_begin; u < u_end; ++seg_idx) {
             Seg sg;
@@ -408,8 +448,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             __half s_next[C::kWT];
 #pragma unroll
             for (int wt = 0; wt < C::kWT; ++wt) s_next[wt] = load_scale_h(p.scales, srow[wt] + ((sg.kb0 * BK) >> 7), p.scale_dtype);
-            for (int j = 0; j < sg.nkb && ok; ++j, ++it) {
-                const int s = it % kNS, sa = it % kNA;
+            for (int j = 0; j < sg.nkb && ok; ++j) {
+                const int s = rr.stage, sa = ra.stage;
                 __half2 sc[C::kWT];
 #pragma unroll
                 for (int wt = 0; wt < C::kWT; ++wt) sc[wt] = __halves2half2(s_next[wt], s_next[wt]);
@@ -418,13 +458,14 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     for (int wt = 0; wt < C::kWT; ++wt)
                         s_next[wt] = load_scale_h(p.scales, srow[wt] + (((sg.kb0 + j + 1) * BK) >> 7), p.scale_dtype);
                 }
-                ok = mbar_wait(bar_full_raw + 8 * s, (uint32_t)(it / kNS) & 1u, s_dead, 16) &&
-                     mbar_wait(bar_empty_a + 8 * sa, ((uint32_t)(it / kNA) & 1u) ^ 1u, s_dead, 32);
+                ok = mbar_wait(bar_full_raw + 8 * s, rr.phase, s_dead, 16) &&
+                     mbar_wait(bar_empty_a + 8 * sa, ra.phase ^ 1u, s_dead, 32);
                 if (!ok) break;
+                tc_fence_after();   // the MMAs that last read this TMEM stage are complete (empty_a): order our stores after them
 #pragma unroll
                 for (int wt = 0; wt < C::kWT; ++wt) {
                     const uint32_t raw_row = s_raw + s * C::kRawBytes + wt * (128 * BK) + r * BK;
-                    const uint32_t a_tile = s_a + sa * C::kABytes + wt * (C::kSlabs * 16384) + a_row_off;
+                    const uint32_t a_dst = t_lane_a + sa * C::kACols + wt * (BK / 2);
 #pragma unroll
                     for (int c = 0; c < kCPT; ++c) {
                         const uint32_t chunk = (uint32_t)(hk * kCPT + c);
@@ -435,15 +476,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         e4m3x4_scaled_hw(q.y, sc[wt], hw[2], hw[3]);
                         e4m3x4_scaled_hw(q.z, sc[wt], hw[4], hw[5]);
                         e4m3x4_scaled_hw(q.w, sc[wt], hw[6], hw[7]);
-                        const uint32_t jj = chunk * 2;  // 16-byte FP16 chunk index along K within the stage
-                        const uint32_t dst = a_tile + (jj >> 3) * 16384;
-                        sts128(dst + (((jj & 7u) ^ r7) << 4), hw[0], hw[1], hw[2], hw[3]);
-                        sts128(dst + ((((jj + 1) & 7u) ^ r7) << 4), hw[4], hw[5], hw[6], hw[7]);
+                        tmem_st8(a_dst + chunk * 8, hw);   // 16 K elements = 8 columns
                     }
                 }
-                fence_async_smem();
+                tmem_wait_st();
+                tc_fence_before();
                 mbar_arrive(bar_full_a + 8 * sa);
                 mbar_arrive(bar_empty_raw + 8 * s);
+                rr.advance(kNS);
+                ra.advance(kNA);
             }
 
             // ---- epilogue of this segment ----
@@ -456,7 +497,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 float* part = p.partial + (int64_t)partial_slot(cta, sg.tile, total_kb, units_per_cta) * kTileFloats;
 #pragma unroll 1
                 for (int c0 = 0; c0 < kColsPerWarp; c0 += 8) {
-                    const int col = ch * kColsPerWarp + c0;
+                    const int col = hk * kColsPerWarp + c0;
                     float g[8], uu[8];
                     tmem_ld8(t_lane + col, g);
                     if (PAIRED) tmem_ld8(t_lane + BT + col, uu);
@@ -490,17 +531,28 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             const int dead_now = s_ticket[1];
             if (!direct && ticket == sg.n_contrib - 1) {
                 __threadfence();
-                for (int idx = td; idx < BT * 128; idx += kDequantThreads) {
-                    const int ml = idx >> 7, nl = idx & 127;
-                    if (ml < sg.rows_valid && n0 + nl < p.N) {
-                        float g = 0.f, uu = 0.f;
-                        for (int cc = sg.first_c; cc < sg.first_c + sg.n_contrib; ++cc) {  // fixed order: deterministic
-                            const float* ps = p.partial + (int64_t)partial_slot(cc, sg.tile, total_kb, units_per_cta) * kTileFloats;
-                            g += __ldcg(&ps[idx]);
-                            if (PAIRED) uu += __ldcg(&ps[BT * 128 + idx]);
+                // four consecutive output features per thread and step; the contributors' slots are read
+                // with independent 16-byte loads (several in flight) and added in ascending CTA order
+                for (int idx4 = td; idx4 < BT * 32; idx4 += kDequantThreads) {
+                    const int ml = idx4 >> 5, nl = (idx4 & 31) * 4;
+                    if (ml >= sg.rows_valid || n0 + nl >= p.N) continue;
+                    float4 g = make_float4(0.f, 0.f, 0.f, 0.f), uu = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                    for (int cc = sg.first_c; cc < sg.first_c + sg.n_contrib; ++cc) {
+                        const float4* ps = reinterpret_cast<const float4*>(
+                            p.partial + (int64_t)partial_slot(cc, sg.tile, total_kb, units_per_cta) * kTileFloats);
+                        const float4 a = __ldcg(&ps[idx4]);
+                        g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+                        if (PAIRED) {
+                            const float4 b = __ldcg(&ps[BT * 32 + idx4]);
+                            uu.x += b.x; uu.y += b.y; uu.z += b.z; uu.w += b.w;
                         }
-                        store_out<PAIRED>(p, sg.row_begin + ml, n0 + nl, g, uu);
                     }
+                    const int row = sg.row_begin + ml, n = n0 + nl;
+                    store_out<PAIRED>(p, row, n, g.x, uu.x);
+                    if (n + 1 < p.N) store_out<PAIRED>(p, row, n + 1, g.y, uu.y);
+                    if (n + 2 < p.N) store_out<PAIRED>(p, row, n + 2, g.z, uu.z);
+                    if (n + 3 < p.N) store_out<PAIRED>(p, row, n + 3, g.w, uu.w);
                 }
                 if (td == 0) p.tickets[sg.tile] = 0u;  // leave the counter clean for the next launch
             }
@@ -618,13 +670,9 @@ int launch_cfg(const TcLaunch& L, cudaStream_t st) {
 
 }  // namespace
 
-int tc_block_k(int bt, bool paired) {
-    (void)bt;
-    (void)paired;
-    return 64;
-}
+int tc_block_k(int bt, bool paired) { return (!paired && bt <= 64) ? 128 : 64; }
 
-int tc_ctas_per_sm(int bt, bool paired) { return (!paired && bt <= 64) ? 2 : 1; }
+int tc_ctas_per_sm(int bt, bool paired) { return (bt * (paired ? 2 : 1) <= 64) ? 2 : 1; }
 
 int tc_grid(int bt, bool paired) { return sm_count() * tc_ctas_per_sm(bt, paired); }
 
@@ -647,9 +695,9 @@ int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st) {
 #define W8A16_TC_CASE(BT_, BK_, P_) return launch_cfg<BT_, BK_, P_>(L, st)
     if (!paired) {
         switch (bt) {
-            case 16: W8A16_TC_CASE(16, 64, false);
-            case 32: W8A16_TC_CASE(32, 64, false);
-            case 64: W8A16_TC_CASE(64, 64, false);
+            case 16: W8A16_TC_CASE(16, 128, false);
+            case 32: W8A16_TC_CASE(32, 128, false);
+            case 64: W8A16_TC_CASE(64, 128, false);
             case 128: W8A16_TC_CASE(128, 64, false);
             case 256: W8A16_TC_CASE(256, 64, false);
         }
@@ -659,7 +707,6 @@ int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st) {
             case 32: W8A16_TC_CASE(32, 64, true);
             case 64: W8A16_TC_CASE(64, 64, true);
             case 128: W8A16_TC_CASE(128, 64, true);
-            case 256: W8A16_TC_CASE(256, 64, true);
         }
     }
 #undef W8A16_TC_CASE
