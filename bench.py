@@ -38,7 +38,7 @@ PREFILL_M = [512, 2048, 8192]
 MOE_CFG = dict(E=128, topk=8, H=2048, I=768)
 NOMINAL_HBM_GBS = 8000.0
 NOMINAL_F16_TFLOPS = 2250.0
-GEMV_MAX_M = 4   # fp8w8a16_linear ALGO_AUTO: M <= 4 -> CUDA-core GEMV, else tcgen05 GEMM
+GEMV_MAX_M = 1   # fp8w8a16_linear ALGO_AUTO: M == 1 -> CUDA-core GEMV, else tcgen05 GEMM
 
 
 def algorithmic_bytes(M: int, N: int, K: int, block_h: int = 128) -> int:

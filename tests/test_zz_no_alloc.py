@@ -45,8 +45,8 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row(lib):
 
 def test_noalloc_rejects_shapes_beyond_its_scratch(lib):
     from vllm_fp8_w8a16_sm70_b200 import _cabi
-    # 4 tokens x 28384 outputs split 2 ways over K needs 64 KiB of counters + 887 KiB of fp32 partial sums
-    N, K, M = 28384, 2048, 4
+    # 4 tokens x 28384 outputs split 3 ways over K needs 64 KiB of counters + 1330 KiB of fp32 partial sums
+    N, K, M = 28384, 8192, 4
     buf = torch.zeros(1 << 20, dtype=torch.uint8, device="cuda")   # never dereferenced: the call is refused first
     p = buf.data_ptr()
     rc = lib.fp8w8a16_linear_noalloc(p, p, p, 0, p, M, N, K, 128, 128, None)

@@ -265,7 +265,7 @@ int fp8w8a16_linear(const uint16_t* x, const uint8_t* w, const void* scales, int
     const __half* xh = reinterpret_cast<const __half*>(x);
     __half* oh = reinterpret_cast<__half*>(out);
     cudaStream_t st = (cudaStream_t)stream;
-    if (algo == FP8W8A16_ALGO_AUTO) algo = (M <= 4) ? FP8W8A16_ALGO_GEMV : FP8W8A16_ALGO_TC;
+    if (algo == FP8W8A16_ALGO_AUTO) algo = (M == 1) ? FP8W8A16_ALGO_GEMV : FP8W8A16_ALGO_TC;
     switch (algo) {
         case FP8W8A16_ALGO_GEMV:
             return launch_gemv(xh, w, scales, scale_dtype, oh, M, N, K, block_h, block_w, workspace, workspace_bytes, st);

@@ -296,17 +296,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     using C = TcCfg<BT, BK, PAIRED>;
     constexpr int kNS = C::kNS, kNA = C::kNA;
 
-    // ---- this CTA's unit range ----
-    const int total_kb = (p.K + BK - 1) / BK;
-    const int n_tt = (p.expert_offsets != nullptr) ? p.tile_offsets[p.num_experts] : p.n_token_tiles;
-    const int n_slabs = (p.N + 127) / 128;
-    const int total_units = n_tt * n_slabs * total_kb;
-    int units_per_cta = (total_units + (int)gridDim.x - 1) / (int)gridDim.x;
-    if (p.no_split) units_per_cta = (units_per_cta + total_kb - 1) / total_kb * total_kb;  // whole tiles only
-    const int cta = blockIdx.x;
-    const int u_begin = cta * units_per_cta;
-    const int u_end = min(total_units, u_begin + units_per_cta);
-    if (u_begin >= u_end) return;  // nothing to do (uniform for the whole CTA, before any barrier exists)
+    // Programmatic dependent launch: let the next kernel of the stream start its own set-up as soon as
+    // this grid's CTAs are resident; it will wait (griddepcontrol.wait) for this grid to finish before
+    // it reads or writes global memory.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     // ---- shared memory carve-up (1024-byte aligned tiles) ----
     extern __shared__ uint8_t smem_dyn[];
@@ -349,7 +342,26 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     const uint32_t tmem_base = *s_tmem;
     const uint32_t tmem_a0 = tmem_base + C::kAccCols;  // first column of the dequantised-operand stages
 
-    if (warp == 0) {
+    // Everything above touched no global memory, so under programmatic dependent launch it may have
+    // overlapped the tail of the previous kernel in the stream.  From here on that kernel's results
+    // (activations, route tables, workspace) are needed.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    // ---- this CTA's unit range ----
+    const int total_kb = (p.K + BK - 1) / BK;
+    const int n_tt = (p.expert_offsets != nullptr) ? p.tile_offsets[p.num_experts] : p.n_token_tiles;
+    const int n_slabs = (p.N + 127) / 128;
+    const int total_units = n_tt * n_slabs * total_kb;
+    int units_per_cta = (total_units + (int)gridDim.x - 1) / (int)gridDim.x;
+    if (p.no_split) units_per_cta = (units_per_cta + total_kb - 1) / total_kb * total_kb;  // whole tiles only
+    const int cta = blockIdx.x;
+    const int u_begin = cta * units_per_cta;
+    const int u_end = min(total_units, u_begin + units_per_cta);
+    const bool has_work = u_begin < u_end;  // uniform for the whole CTA
+
+    if (!has_work) {
+        // nothing to do: fall through to the teardown (TMEM must still be returned)
+    } else if (warp == 0) {
         // ================= TMA producer =================
         if (lane == 0) {
             Ring ring;
@@ -444,19 +456,25 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 n = min(n, p.w_rows_per_expert - 1);
                 srow[wt] = (int64_t)sg.expert * p.scale_expert_stride + (int64_t)(n / p.block_h) * p.Kb;
             }
-            // software-pipelined scale fetch: the value for K block j + 1 is requested while block j is converted
-            __half s_next[C::kWT];
+            // software-pipelined scale fetch: the values for K blocks j + 1 and j + 2 are in flight while
+            // block j is converted (an L2 round trip is longer than one K block)
+            const int kb_last = sg.kb0 + sg.nkb - 1;
+            __half s_cur[C::kWT], s_nx1[C::kWT];
 #pragma unroll
-            for (int wt = 0; wt < C::kWT; ++wt) s_next[wt] = load_scale_h(p.scales, srow[wt] + ((sg.kb0 * BK) >> 7), p.scale_dtype);
+            for (int wt = 0; wt < C::kWT; ++wt) {
+                s_cur[wt] = load_scale_h(p.scales, srow[wt] + ((sg.kb0 * BK) >> 7), p.scale_dtype);
+                s_nx1[wt] = load_scale_h(p.scales, srow[wt] + ((min(sg.kb0 + 1, kb_last) * BK) >> 7), p.scale_dtype);
+            }
             for (int j = 0; j < sg.nkb && ok; ++j) {
                 const int s = rr.stage, sa = ra.stage;
                 __half2 sc[C::kWT];
+                __half s_nx2[C::kWT];
 #pragma unroll
-                for (int wt = 0; wt < C::kWT; ++wt) sc[wt] = __halves2half2(s_next[wt], s_next[wt]);
-                if (j + 1 < sg.nkb) {
-#pragma unroll
-                    for (int wt = 0; wt < C::kWT; ++wt)
-                        s_next[wt] = load_scale_h(p.scales, srow[wt] + (((sg.kb0 + j + 1) * BK) >> 7), p.scale_dtype);
+                for (int wt = 0; wt < C::kWT; ++wt) {
+                    sc[wt] = __halves2half2(s_cur[wt], s_cur[wt]);
+                    s_nx2[wt] = load_scale_h(p.scales, srow[wt] + ((min(sg.kb0 + j + 2, kb_last) * BK) >> 7), p.scale_dtype);
+                    s_cur[wt] = s_nx1[wt];
+                    s_nx1[wt] = s_nx2[wt];
                 }
                 ok = mbar_wait(bar_full_raw + 8 * s, rr.phase, s_dead, 16) &&
                      mbar_wait(bar_empty_a + 8 * sa, ra.phase ^ 1u, s_dead, 32);
@@ -664,7 +682,18 @@ int launch_cfg(const TcLaunch& L, cudaStream_t st) {
     int64_t g = (int64_t)sm_count() * C::kCtasPerSm;
     if (L.max_units < g) g = L.max_units;
     if (g < 1) g = 1;
-    k_gemm_tc<BT, BK, PAIRED><<<(unsigned)g, kThreadsTc, C::kSmemBytes, st>>>(map_w, map_x, L.p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)g);
+    cfg.blockDim = dim3(kThreadsTc);
+    cfg.dynamicSmemBytes = C::kSmemBytes;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // overlap our set-up with the previous kernel's tail
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, k_gemm_tc<BT, BK, PAIRED>, map_w, map_x, L.p);
+    if (le != cudaSuccess) return fail(FP8W8A16_ERR_CUDA, "gemm_tc launch failed: %s", cudaGetErrorString(le));
     return check_launch("gemm_tc");
 }
 
