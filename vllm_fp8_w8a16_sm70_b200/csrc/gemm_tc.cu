@@ -43,6 +43,20 @@ namespace w8a16 {
 
 __device__ int g_tc_status = 0;  // sticky error bits set by bounded waits (0 = healthy)
 
+#ifdef W8A16_TC_TRACE
+// Debug build only: per-K-block timestamps of the three roles of CTA 0 (globaltimer, ns).
+__device__ unsigned long long g_tc_trace[3][256][6];
+__device__ unsigned long long g_tc_cta[512][4];   // per CTA: entry, after set-up + dependency wait, main loop done, exit
+#define TC_TRACE(role, idx, slot) do { if (blockIdx.x == 0 && (idx) < 256) g_tc_trace[role][idx][slot] = globaltimer_ns_raw(); } while (0)
+__device__ __forceinline__ unsigned long long globaltimer_ns_raw() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#else
+#define TC_TRACE(role, idx, slot) do { } while (0)
+#endif
+
 namespace {
 
 constexpr int kThreadsTc = 320;
@@ -132,6 +146,17 @@ __device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, ui
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
         ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Accumulating form with a constant-true predicate: nothing but the MMA itself is issued.  The single
+// issuing thread is the narrowest point of the decode pipeline (a lone warp issues one instruction
+// every few cycles), so every instruction saved per MMA counts.
+__device__ __forceinline__ void umma_f16_ts_acc(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.eq.u32 p, 1, 1;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc)
         : "memory");
 }
 // Eight 32-bit registers (16 FP16 values, K ascending, even K in the low half) -> eight consecutive
@@ -300,6 +325,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     // this grid's CTAs are resident; it will wait (griddepcontrol.wait) for this grid to finish before
     // it reads or writes global memory.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+#ifdef W8A16_TC_TRACE
+    if (threadIdx.x == 0 && blockIdx.x < 512) g_tc_cta[blockIdx.x][0] = globaltimer_ns_raw();
+#endif
 
     // ---- shared memory carve-up (1024-byte aligned tiles) ----
     extern __shared__ uint8_t smem_dyn[];
@@ -346,6 +374,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     // overlapped the tail of the previous kernel in the stream.  From here on that kernel's results
     // (activations, route tables, workspace) are needed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
+#ifdef W8A16_TC_TRACE
+    if (threadIdx.x == 0 && blockIdx.x < 512) g_tc_cta[blockIdx.x][1] = globaltimer_ns_raw();
+#endif
 
     // ---- this CTA's unit range ----
     const int total_kb = (p.K + BK - 1) / BK;
@@ -376,6 +407,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                          mbar_wait(bar_empty_x + 8 * s, ring.phase ^ 1u, s_dead, 2);
                     if (!ok) break;
                     const int k0 = (sg.kb0 + j) * BK;
+                    TC_TRACE(0, u - u_begin + j, 0);
                     mbar_arrive_expect_tx(bar_full_raw + 8 * s, C::kRawBytes);
                     tma_load_2d(s_raw + s * C::kRawBytes, &map_w, bar_full_raw + 8 * s, k0, w_row);
                     if (PAIRED) tma_load_2d(s_raw + s * C::kRawBytes + 128 * BK, &map_w, bar_full_raw + 8 * s, k0, w_row + p.pair_offset);
@@ -401,22 +433,30 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     ok = mbar_wait(bar_full_a + 8 * ra.stage, ra.phase, s_dead, 4) &&
                          mbar_wait(bar_full_x + 8 * rx.stage, rx.phase, s_dead, 8);
                     if (!ok) break;
+                    TC_TRACE(1, u - u_begin + j, 0);
                     tc_fence_after();
                     const uint32_t a_col = tmem_a0 + ra.stage * C::kACols;
-                    const uint32_t x_st = s_x + rx.stage * C::kXBytes;
+                    // one descriptor per K block; the 16-element K steps only add to its start-address field
+                    const uint64_t db0 = make_desc_sw128(s_x + rx.stage * C::kXBytes);
 #pragma unroll
                     for (int sl = 0; sl < C::kSlabs; ++sl) {
 #pragma unroll
                         for (int kk = 0; kk < 4; ++kk) {
-                            const uint32_t acc = (j > 0 || sl > 0 || kk > 0) ? 1u : 0u;  // first MMA of a segment overwrites
-                            const uint64_t db = make_desc_sw128(x_st + sl * (BT * 128) + kk * 32);
+                            const uint64_t db = db0 + (uint64_t)((sl * (BT * 128) + kk * 32) >> 4);
                             const uint32_t a_k = a_col + (sl * 4 + kk) * 8;           // 16 K elements = 8 columns
-                            umma_f16_ts(tmem_base, a_k, db, idesc, acc);
-                            if (PAIRED) umma_f16_ts(tmem_base + BT, a_k + BK / 2, db, idesc, acc);
+                            if (sl == 0 && kk == 0) {
+                                const uint32_t acc = j > 0 ? 1u : 0u;                 // first MMA of a segment overwrites
+                                umma_f16_ts(tmem_base, a_k, db, idesc, acc);
+                                if (PAIRED) umma_f16_ts(tmem_base + BT, a_k + BK / 2, db, idesc, acc);
+                            } else {
+                                umma_f16_ts_acc(tmem_base, a_k, db, idesc);
+                                if (PAIRED) umma_f16_ts_acc(tmem_base + BT, a_k + BK / 2, db, idesc);
+                            }
                         }
                     }
                     umma_commit(bar_empty_a + 8 * ra.stage);
                     umma_commit(bar_empty_x + 8 * rx.stage);
+                    TC_TRACE(1, u - u_begin + j, 1);
                     ra.advance(kNA);
                     rx.advance(kNS);
                 }
@@ -442,6 +482,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 
         Ring rr, ra;   // raw-tile ring (shared memory) and dequantised-operand ring (TMEM)
         int seg_idx = 0;
+        int tr_i = 0;  // K blocks converted so far (index of the debug trace; unused otherwise)
+        (void)tr_i;
         bool ok = true;
         for (int u = u_begin; u < u_end; ++seg_idx) {
             Seg sg;
@@ -476,9 +518,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     s_cur[wt] = s_nx1[wt];
                     s_nx1[wt] = s_nx2[wt];
                 }
-                ok = mbar_wait(bar_full_raw + 8 * s, rr.phase, s_dead, 16) &&
-                     mbar_wait(bar_empty_a + 8 * sa, ra.phase ^ 1u, s_dead, 32);
+                if (td == 0) TC_TRACE(2, tr_i, 0);
+                ok = mbar_wait(bar_full_raw + 8 * s, rr.phase, s_dead, 16);
+                if (td == 0) TC_TRACE(2, tr_i, 1);
+                ok = ok && mbar_wait(bar_empty_a + 8 * sa, ra.phase ^ 1u, s_dead, 32);
                 if (!ok) break;
+                if (td == 0) TC_TRACE(2, tr_i, 2);
                 tc_fence_after();   // the MMAs that last read this TMEM stage are complete (empty_a): order our stores after them
 #pragma unroll
                 for (int wt = 0; wt < C::kWT; ++wt) {
@@ -497,10 +542,14 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         tmem_st8(a_dst + chunk * 8, hw);   // 16 K elements = 8 columns
                     }
                 }
+                if (td == 0) TC_TRACE(2, tr_i, 3);
                 tmem_wait_st();
+                if (td == 0) TC_TRACE(2, tr_i, 4);
                 tc_fence_before();
                 mbar_arrive(bar_full_a + 8 * sa);
                 mbar_arrive(bar_empty_raw + 8 * s);
+                if (td == 0) TC_TRACE(2, tr_i, 5);
+                ++tr_i;
                 rr.advance(kNS);
                 ra.advance(kNA);
             }
@@ -578,6 +627,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         }
     }
 
+#ifdef W8A16_TC_TRACE
+    if (threadIdx.x == 64 && blockIdx.x < 512) g_tc_cta[blockIdx.x][2] = globaltimer_ns_raw();
+#endif
     // ---- teardown: every thread arrives here, also after a timed-out wait ----
     if (*s_dead) {
         // let copies and MMAs that are still in flight land before shared memory and TMEM go away
@@ -590,6 +642,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
     }
+#ifdef W8A16_TC_TRACE
+    if (threadIdx.x == 0 && blockIdx.x < 512) g_tc_cta[blockIdx.x][3] = globaltimer_ns_raw();
+#endif
 }
 
 // ---- host side -----------------------------------------------------------------------------------
@@ -741,6 +796,15 @@ int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st) {
 #undef W8A16_TC_CASE
     return fail(FP8W8A16_ERR_UNSUPPORTED, "gemm_tc: unsupported token tile %d", bt);
 }
+
+#ifdef W8A16_TC_TRACE
+extern "C" int w8a16_debug_read_trace(unsigned long long* host, size_t bytes) {
+    return (int)cudaMemcpyFromSymbol(host, g_tc_trace, bytes);
+}
+extern "C" int w8a16_debug_read_cta(unsigned long long* host, size_t bytes) {
+    return (int)cudaMemcpyFromSymbol(host, g_tc_cta, bytes);
+}
+#endif
 
 int tc_read_status(int* out, int reset) {
     int v = 0;
