@@ -209,8 +209,10 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // ---- compile-time configuration ------------------------------------------------------------------
-// TMEM columns of one CTA: [0, kAccCols) fp32 accumulators (BT per weight tile), then kNA stages of
-// the dequantised FP16 A operand (BK / 2 columns per weight tile: two K elements per 32-bit cell).
+// TMEM columns of one CTA: kAccBufs accumulator buffers of kAccCols fp32 columns (BT per weight
+// tile; two buffers where they fit, so the epilogue of one segment overlaps the MMAs of the next),
+// then kNA stages of the dequantised FP16 A operand (BK / 2 columns per weight tile: two K elements
+// per 32-bit cell).
 template <int BT, int BK, bool PAIRED>
 struct TcCfg {
     static constexpr int kWT = PAIRED ? 2 : 1;                 // weight tiles per stage (gate + up)
@@ -223,14 +225,17 @@ struct TcCfg {
     // each): one CTA's prologue / epilogue hides behind the other's main loop, 16 warps dequantise.
     static constexpr int kCtasPerSm = (BT * kWT <= 64) ? 2 : 1;
     static constexpr int kTmemBudget = 512 / kCtasPerSm;
-    static constexpr int kNAraw = (kTmemBudget - kAccCols) / kACols;
+    static constexpr int kAccBufs = (2 * kAccCols + 2 * kACols <= kTmemBudget) ? 2 : 1;
+    static constexpr int kNAraw = (kTmemBudget - kAccBufs * kAccCols) / kACols;
     static constexpr int kNA = kNAraw > 4 ? 4 : kNAraw;        // dequantised-operand stages (TMEM)
-    static constexpr int kUsedCols = kAccCols + kNA * kACols;
+    static constexpr int kUsedCols = kAccBufs * kAccCols + kNA * kACols;
+    // K blocks of the NEXT segment that are converted before the previous segment's epilogue runs
+    static constexpr int kDefer = kAccBufs == 2 ? kNA : 0;
     static constexpr int kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128 : kUsedCols <= 256 ? 256 : 512;
     static constexpr int kBudget = (kCtasPerSm == 2 ? 112 : 225) * 1024 - 2048;  // dynamic shared memory we allow ourselves
     static constexpr int kNSraw = kBudget / (kRawBytes + kXBytes);
     static constexpr int kNS = kNSraw > 8 ? 8 : kNSraw;        // TMA ring stages
-    static constexpr int kNumBars = 4 * kNS + 2 * kNA + 1;
+    static constexpr int kNumBars = 4 * kNS + 2 * kNA + 2;
     static constexpr int kSmemBytes = 1024 + kNS * (kRawBytes + kXBytes) + kNumBars * 8 + 64;
     static_assert(kNS >= 2, "not enough shared memory for a 2-stage TMA ring");
     static_assert(kNA >= 2, "not enough TMEM for two dequantised stages");
@@ -358,6 +363,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             mbar_init(bar_empty_a + 8 * i, 1);
         }
         mbar_init(bar_acc, 1);
+        mbar_init(bar_acc + 8, 1);
         *s_dead = 0;
         s_ticket[0] = 0;
         s_ticket[1] = 0;
@@ -368,26 +374,55 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
-    const uint32_t tmem_a0 = tmem_base + C::kAccCols;  // first column of the dequantised-operand stages
+    const uint32_t tmem_a0 = tmem_base + C::kAccBufs * C::kAccCols;  // first column of the dequantised-operand stages
 
-    // Everything above touched no global memory, so under programmatic dependent launch it may have
-    // overlapped the tail of the previous kernel in the stream.  From here on that kernel's results
-    // (activations, route tables, workspace) are needed.
+    // ---- this CTA's unit range ----
+    // Dense problems know it from the launch parameters alone; grouped ones read the tile count from
+    // the route table, which the previous kernel wrote, so they must wait for it first.
+    const bool grouped = p.expert_offsets != nullptr;
+    const int total_kb = (p.K + BK - 1) / BK;
+    const int n_slabs = (p.N + 127) / 128;
+    const int cta = blockIdx.x;
+    int n_tt = p.n_token_tiles, total_units = 0, units_per_cta = 0, u_begin = 0, u_end = 0;
+    auto set_range = [&]() {
+        total_units = n_tt * n_slabs * total_kb;
+        units_per_cta = (total_units + (int)gridDim.x - 1) / (int)gridDim.x;
+        if (p.no_split) units_per_cta = (units_per_cta + total_kb - 1) / total_kb * total_kb;  // whole tiles only
+        u_begin = cta * units_per_cta;
+        u_end = min(total_units, u_begin + units_per_cta);
+    };
+    if (!grouped) set_range();
+
+    // The weights are constants of the model, not results of the previous kernel: the producer requests
+    // the first ring of weight tiles BEFORE the dependency wait, so that under programmatic dependent
+    // launch the HBM latency of the first tiles hides behind the previous kernel's tail.
+    int w_preissued = 0;
+    if (!grouped && warp == 0 && lane == 0) {
+        for (int u = u_begin; u < u_end && w_preissued < kNS;) {
+            Seg sg;
+            get_seg<BT>(p, u, u_end, total_kb, n_tt, units_per_cta, sg);
+            const int w_row = sg.slab * 128;
+            for (int j = 0; j < sg.nkb && w_preissued < kNS; ++j, ++w_preissued) {
+                const int s = w_preissued;  // ring is empty: stage index == unit index, no wait needed
+                mbar_arrive_expect_tx(bar_full_raw + 8 * s, C::kRawBytes);
+                tma_load_2d(s_raw + s * C::kRawBytes, &map_w, bar_full_raw + 8 * s, (sg.kb0 + j) * BK, w_row);
+                if (PAIRED) tma_load_2d(s_raw + s * C::kRawBytes + 128 * BK, &map_w, bar_full_raw + 8 * s, (sg.kb0 + j) * BK, w_row + p.pair_offset);
+            }
+            u += sg.nkb;
+        }
+    }
+
+    // Everything above read only launch parameters and model weights, so under programmatic dependent
+    // launch it may have overlapped the tail of the previous kernel in the stream.  From here on that
+    // kernel's results (activations, route tables, workspace) are needed.
     asm volatile("griddepcontrol.wait;" ::: "memory");
 #ifdef W8A16_TC_TRACE
     if (threadIdx.x == 0 && blockIdx.x < 512) g_tc_cta[blockIdx.x][1] = globaltimer_ns_raw();
 #endif
-
-    // ---- this CTA's unit range ----
-    const int total_kb = (p.K + BK - 1) / BK;
-    const int n_tt = (p.expert_offsets != nullptr) ? p.tile_offsets[p.num_experts] : p.n_token_tiles;
-    const int n_slabs = (p.N + 127) / 128;
-    const int total_units = n_tt * n_slabs * total_kb;
-    int units_per_cta = (total_units + (int)gridDim.x - 1) / (int)gridDim.x;
-    if (p.no_split) units_per_cta = (units_per_cta + total_kb - 1) / total_kb * total_kb;  // whole tiles only
-    const int cta = blockIdx.x;
-    const int u_begin = cta * units_per_cta;
-    const int u_end = min(total_units, u_begin + units_per_cta);
+    if (grouped) {
+        n_tt = p.tile_offsets[p.num_experts];
+        set_range();
+    }
     const bool has_work = u_begin < u_end;  // uniform for the whole CTA
 
     if (!has_work) {
@@ -397,20 +432,24 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         if (lane == 0) {
             Ring ring;
             bool ok = true;
+            int it = 0;   // K blocks handled so far; the first w_preissued of them already have their weight tile in flight
             for (int u = u_begin; u < u_end && ok;) {
                 Seg sg;
                 get_seg<BT>(p, u, u_end, total_kb, n_tt, units_per_cta, sg);
                 const int w_row = sg.expert * p.w_rows_per_expert + sg.slab * 128;
-                for (int j = 0; j < sg.nkb; ++j) {
+                for (int j = 0; j < sg.nkb; ++j, ++it) {
                     const int s = ring.stage;
-                    ok = mbar_wait(bar_empty_raw + 8 * s, ring.phase ^ 1u, s_dead, 1) &&
-                         mbar_wait(bar_empty_x + 8 * s, ring.phase ^ 1u, s_dead, 2);
-                    if (!ok) break;
                     const int k0 = (sg.kb0 + j) * BK;
-                    TC_TRACE(0, u - u_begin + j, 0);
-                    mbar_arrive_expect_tx(bar_full_raw + 8 * s, C::kRawBytes);
-                    tma_load_2d(s_raw + s * C::kRawBytes, &map_w, bar_full_raw + 8 * s, k0, w_row);
-                    if (PAIRED) tma_load_2d(s_raw + s * C::kRawBytes + 128 * BK, &map_w, bar_full_raw + 8 * s, k0, w_row + p.pair_offset);
+                    if (it >= w_preissued) {
+                        ok = mbar_wait(bar_empty_raw + 8 * s, ring.phase ^ 1u, s_dead, 1);
+                        if (!ok) break;
+                        TC_TRACE(0, it, 0);
+                        mbar_arrive_expect_tx(bar_full_raw + 8 * s, C::kRawBytes);
+                        tma_load_2d(s_raw + s * C::kRawBytes, &map_w, bar_full_raw + 8 * s, k0, w_row);
+                        if (PAIRED) tma_load_2d(s_raw + s * C::kRawBytes + 128 * BK, &map_w, bar_full_raw + 8 * s, k0, w_row + p.pair_offset);
+                    }
+                    ok = mbar_wait(bar_empty_x + 8 * s, ring.phase ^ 1u, s_dead, 2);
+                    if (!ok) break;
                     mbar_arrive_expect_tx(bar_full_x + 8 * s, C::kXBytes);
 #pragma unroll
                     for (int sl = 0; sl < C::kSlabs; ++sl)
@@ -426,7 +465,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             constexpr uint32_t idesc = make_idesc_f16(BT);
             Ring rx, ra;
             bool ok = true;
-            for (int u = u_begin; u < u_end && ok;) {
+            int si = 0;   // segment index: selects the accumulator buffer
+            for (int u = u_begin; u < u_end && ok; ++si) {
+                const uint32_t d_acc = tmem_base + (uint32_t)((si % C::kAccBufs) * C::kAccCols);
                 const int tile = u / total_kb;
                 const int nkb = min(total_kb - (u - tile * total_kb), u_end - u);
                 for (int j = 0; j < nkb; ++j) {
@@ -446,11 +487,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                             const uint32_t a_k = a_col + (sl * 4 + kk) * 8;           // 16 K elements = 8 columns
                             if (sl == 0 && kk == 0) {
                                 const uint32_t acc = j > 0 ? 1u : 0u;                 // first MMA of a segment overwrites
-                                umma_f16_ts(tmem_base, a_k, db, idesc, acc);
-                                if (PAIRED) umma_f16_ts(tmem_base + BT, a_k + BK / 2, db, idesc, acc);
+                                umma_f16_ts(d_acc, a_k, db, idesc, acc);
+                                if (PAIRED) umma_f16_ts(d_acc + BT, a_k + BK / 2, db, idesc, acc);
                             } else {
-                                umma_f16_ts_acc(tmem_base, a_k, db, idesc);
-                                if (PAIRED) umma_f16_ts_acc(tmem_base + BT, a_k + BK / 2, db, idesc);
+                                umma_f16_ts_acc(d_acc, a_k, db, idesc);
+                                if (PAIRED) umma_f16_ts_acc(d_acc + BT, a_k + BK / 2, db, idesc);
                             }
                         }
                     }
@@ -460,7 +501,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     ra.advance(kNA);
                     rx.advance(kNS);
                 }
-                if (ok) umma_commit(bar_acc);  // accumulators of this segment are complete
+                if (ok) umma_commit(bar_acc + 8 * (si % C::kAccBufs));  // accumulators of this segment are complete
                 u += nkb;
             }
         }
@@ -476,16 +517,98 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         const uint32_t r7 = (uint32_t)(r & 7);
         const int n_local = r;
         const uint32_t t_lane = tmem_base + ((uint32_t)(q4 * 32) << 16);
-        const uint32_t t_lane_a = t_lane + C::kAccCols;
+        const uint32_t t_lane_a = t_lane + C::kAccBufs * C::kAccCols;
         constexpr int kColsPerWarp = BT / 2;
         constexpr int kTileFloats = C::kWT * BT * 128;
 
         Ring rr, ra;   // raw-tile ring (shared memory) and dequantised-operand ring (TMEM)
-        int seg_idx = 0;
         int tr_i = 0;  // K blocks converted so far (index of the debug trace; unused otherwise)
         (void)tr_i;
         bool ok = true;
-        for (int u = u_begin; u < u_end; ++seg_idx) {
+
+        // Epilogue of one finished segment: TMEM -> registers -> FP16 output, or fp32 partial tile + ticket
+        // + (for the last contributor) the fixed-order reduction.  Returns the CTA-wide "dead" flag that
+        // thread 0 publishes; every one of the 256 threads calls it once per segment and takes both
+        // barriers inside, whatever its own `ok` says, so a timed-out wait can never strand the others.
+        auto epilogue = [&](const Seg& sg, int si) -> int {
+            const int n0 = sg.slab * 128;
+            const uint32_t t_acc = t_lane + (uint32_t)((si % C::kAccBufs) * C::kAccCols);
+            if (ok) ok = mbar_wait(bar_acc + 8 * (si % C::kAccBufs), (uint32_t)(si / C::kAccBufs) & 1u, s_dead, 64);
+            ok = __all_sync(0xFFFFFFFFu, ok) != 0;  // tcgen05.ld is warp-collective: keep the warp together
+            const bool direct = (sg.n_contrib == 1);
+            if (ok) {
+                tc_fence_after();
+                const int n = n0 + n_local;
+                float* part = p.partial + (int64_t)partial_slot(cta, sg.tile, total_kb, units_per_cta) * kTileFloats;
+#pragma unroll 1
+                for (int c0 = 0; c0 < kColsPerWarp; c0 += 8) {
+                    const int col = hk * kColsPerWarp + c0;
+                    float g[8], uu[8];
+                    tmem_ld8(t_acc + col, g);
+                    if (PAIRED) tmem_ld8(t_acc + BT + col, uu);
+                    if (direct) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (col + j < sg.rows_valid && n < p.N)
+                                store_out<PAIRED>(p, sg.row_begin + col + j, n, g[j], PAIRED ? uu[j] : 0.f);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            __stcg(&part[(col + j) * 128 + n_local], g[j]);
+                            if (PAIRED) __stcg(&part[(BT + col + j) * 128 + n_local], uu[j]);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            // Hand-off.  All 256 threads take both barriers in every segment, whatever happened above,
+            // and act only on values that thread 0 publishes between them, so that a timed-out wait
+            // somewhere in the CTA can never strand part of it at a barrier.
+            if (!direct) __threadfence();
+            epi_bar_sync();
+            if (td == 0) {
+                const int dead = *s_dead;
+                s_ticket[0] = (!direct && !dead) ? (int)atomicAdd(&p.tickets[sg.tile], 1u) : -1;
+                s_ticket[1] = dead;
+            }
+            epi_bar_sync();
+            const int ticket = s_ticket[0];
+            const int dead_now = s_ticket[1];
+            if (!direct && ticket == sg.n_contrib - 1) {
+                __threadfence();
+                // four consecutive output features per thread and step; the contributors' slots are read
+                // with independent 16-byte loads (several in flight) and added in ascending CTA order
+                for (int idx4 = td; idx4 < BT * 32; idx4 += kDequantThreads) {
+                    const int ml = idx4 >> 5, nl = (idx4 & 31) * 4;
+                    if (ml >= sg.rows_valid || n0 + nl >= p.N) continue;
+                    float4 g = make_float4(0.f, 0.f, 0.f, 0.f), uu = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                    for (int cc = sg.first_c; cc < sg.first_c + sg.n_contrib; ++cc) {
+                        const float4* ps = reinterpret_cast<const float4*>(
+                            p.partial + (int64_t)partial_slot(cc, sg.tile, total_kb, units_per_cta) * kTileFloats);
+                        const float4 a = __ldcg(&ps[idx4]);
+                        g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+                        if (PAIRED) {
+                            const float4 b = __ldcg(&ps[BT * 32 + idx4]);
+                            uu.x += b.x; uu.y += b.y; uu.z += b.z; uu.w += b.w;
+                        }
+                    }
+                    const int row = sg.row_begin + ml, n = n0 + nl;
+                    store_out<PAIRED>(p, row, n, g.x, uu.x);
+                    if (n + 1 < p.N) store_out<PAIRED>(p, row, n + 1, g.y, uu.y);
+                    if (n + 2 < p.N) store_out<PAIRED>(p, row, n + 2, g.z, uu.z);
+                    if (n + 3 < p.N) store_out<PAIRED>(p, row, n + 3, g.w, uu.w);
+                }
+                if (td == 0) p.tickets[sg.tile] = 0u;  // leave the counter clean for the next launch
+            }
+            return dead_now;
+        };
+
+        Seg pend;          // finished segment whose epilogue is deferred (double-buffered accumulators)
+        int pend_i = -1;
+        int si = 0;
+        int stop = 0;
+        for (int u = u_begin; u < u_end; ++si) {
             Seg sg;
             get_seg<BT>(p, u, u_end, total_kb, n_tt, units_per_cta, sg);
             u += sg.nkb;
@@ -552,79 +675,30 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 ++tr_i;
                 rr.advance(kNS);
                 ra.advance(kNA);
+                if (C::kDefer > 0 && pend_i >= 0 && j + 1 == min(C::kDefer, sg.nkb)) {
+                    // the MMA warp now has work queued for this segment: drain the previous one meanwhile
+                    stop = epilogue(pend, pend_i);
+                    pend_i = -1;
+                    if (stop) break;
+                }
             }
 
-            // ---- epilogue of this segment ----
-            if (ok) ok = mbar_wait(bar_acc, (uint32_t)seg_idx & 1u, s_dead, 64);
-            ok = __all_sync(0xFFFFFFFFu, ok) != 0;  // tcgen05.ld is warp-collective: keep the warp together
-            const bool direct = (sg.n_contrib == 1);
-            if (ok) {
-                tc_fence_after();
-                const int n = n0 + n_local;
-                float* part = p.partial + (int64_t)partial_slot(cta, sg.tile, total_kb, units_per_cta) * kTileFloats;
-#pragma unroll 1
-                for (int c0 = 0; c0 < kColsPerWarp; c0 += 8) {
-                    const int col = hk * kColsPerWarp + c0;
-                    float g[8], uu[8];
-                    tmem_ld8(t_lane + col, g);
-                    if (PAIRED) tmem_ld8(t_lane + BT + col, uu);
-                    if (direct) {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j)
-                            if (col + j < sg.rows_valid && n < p.N)
-                                store_out<PAIRED>(p, sg.row_begin + col + j, n, g[j], PAIRED ? uu[j] : 0.f);
-                    } else {
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) {
-                            __stcg(&part[(col + j) * 128 + n_local], g[j]);
-                            if (PAIRED) __stcg(&part[(BT + col + j) * 128 + n_local], uu[j]);
-                        }
-                    }
-                }
+
+            if (stop) break;
+            if (pend_i >= 0) {   // only reached when a wait timed out inside the loop above
+                stop = epilogue(pend, pend_i);
+                pend_i = -1;
+                if (stop) break;
             }
-            tc_fence_before();
-            // Hand-off.  All 256 threads take both barriers in every segment, whatever happened above,
-            // and act only on values that thread 0 publishes between them, so that a timed-out wait
-            // somewhere in the CTA can never strand part of it at a barrier.
-            if (!direct) __threadfence();
-            epi_bar_sync();
-            if (td == 0) {
-                const int dead = *s_dead;
-                s_ticket[0] = (!direct && !dead) ? (int)atomicAdd(&p.tickets[sg.tile], 1u) : -1;
-                s_ticket[1] = dead;
+            if (C::kDefer > 0) {
+                pend = sg;
+                pend_i = si;
+            } else {
+                stop = epilogue(sg, si);
+                if (stop) break;
             }
-            epi_bar_sync();
-            const int ticket = s_ticket[0];
-            const int dead_now = s_ticket[1];
-            if (!direct && ticket == sg.n_contrib - 1) {
-                __threadfence();
-                // four consecutive output features per thread and step; the contributors' slots are read
-                // with independent 16-byte loads (several in flight) and added in ascending CTA order
-                for (int idx4 = td; idx4 < BT * 32; idx4 += kDequantThreads) {
-                    const int ml = idx4 >> 5, nl = (idx4 & 31) * 4;
-                    if (ml >= sg.rows_valid || n0 + nl >= p.N) continue;
-                    float4 g = make_float4(0.f, 0.f, 0.f, 0.f), uu = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-                    for (int cc = sg.first_c; cc < sg.first_c + sg.n_contrib; ++cc) {
-                        const float4* ps = reinterpret_cast<const float4*>(
-                            p.partial + (int64_t)partial_slot(cc, sg.tile, total_kb, units_per_cta) * kTileFloats);
-                        const float4 a = __ldcg(&ps[idx4]);
-                        g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
-                        if (PAIRED) {
-                            const float4 b = __ldcg(&ps[BT * 32 + idx4]);
-                            uu.x += b.x; uu.y += b.y; uu.z += b.z; uu.w += b.w;
-                        }
-                    }
-                    const int row = sg.row_begin + ml, n = n0 + nl;
-                    store_out<PAIRED>(p, row, n, g.x, uu.x);
-                    if (n + 1 < p.N) store_out<PAIRED>(p, row, n + 1, g.y, uu.y);
-                    if (n + 2 < p.N) store_out<PAIRED>(p, row, n + 2, g.z, uu.z);
-                    if (n + 3 < p.N) store_out<PAIRED>(p, row, n + 3, g.w, uu.w);
-                }
-                if (td == 0) p.tickets[sg.tile] = 0u;  // leave the counter clean for the next launch
-            }
-            if (dead_now) break;
         }
+        if (!stop && pend_i >= 0) epilogue(pend, pend_i);
     }
 
 #ifdef W8A16_TC_TRACE
