@@ -59,7 +59,7 @@ __device__ __forceinline__ unsigned long long globaltimer_ns_raw() {
 
 namespace {
 
-constexpr int kThreadsTc = 320;
+constexpr int kThreadsTc = 352;   // warp 0 TMA, warp 1 MMA, warps 2-9 dequant + epilogue, warp 10 second MMA issuer
 constexpr int kDequantThreads = 256;
 constexpr unsigned long long kTimeoutNs = 2000000000ull;
 
@@ -220,7 +220,11 @@ struct TcCfg {
     static constexpr int kRawBytes = 128 * BK * kWT;           // FP8 tile(s)
     static constexpr int kXBytes = BT * BK * 2;                // FP16 activation tile
     static constexpr int kACols = (BK / 2) * kWT;              // TMEM columns of one dequantised stage
-    static constexpr int kAccCols = BT * kWT;
+    // One thread can start a tcgen05.mma only every ~56 cycles, far longer than a narrow MMA runs, so
+    // for small token tiles TWO warps issue: each takes half of the 16-element K steps of every K block
+    // and accumulates into its own TMEM columns; the epilogue adds the two halves in fixed order.
+    static constexpr int kIssuers = (BT * kWT <= 128 && BT <= 64) ? 2 : 1;
+    static constexpr int kAccCols = BT * kWT * kIssuers;       // one accumulator buffer
     // Small token tiles are sized so that TWO CTAs share an SM (half of shared memory and of TMEM
     // each): one CTA's prologue / epilogue hides behind the other's main loop, 16 warps dequantise.
     static constexpr int kCtasPerSm = (BT * kWT <= 64) ? 2 : 1;
@@ -356,14 +360,14 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             mbar_init(bar_full_raw + 8 * i, 1);
             mbar_init(bar_empty_raw + 8 * i, kDequantThreads);
             mbar_init(bar_full_x + 8 * i, 1);
-            mbar_init(bar_empty_x + 8 * i, 1);
+            mbar_init(bar_empty_x + 8 * i, C::kIssuers);
         }
         for (int i = 0; i < kNA; ++i) {
             mbar_init(bar_full_a + 8 * i, kDequantThreads);
-            mbar_init(bar_empty_a + 8 * i, 1);
+            mbar_init(bar_empty_a + 8 * i, C::kIssuers);
         }
-        mbar_init(bar_acc, 1);
-        mbar_init(bar_acc + 8, 1);
+        mbar_init(bar_acc, C::kIssuers);
+        mbar_init(bar_acc + 8, C::kIssuers);
         *s_dead = 0;
         s_ticket[0] = 0;
         s_ticket[1] = 0;
@@ -459,45 +463,47 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 u += sg.nkb;
             }
         }
-    } else if (warp == 1) {
-        // ================= MMA issuer =================
-        if (lane == 0) {
+    } else if (warp == 1 || warp == 10) {
+        // ================= MMA issuer(s) =================
+        const int issuer = warp == 1 ? 0 : 1;
+        if (lane == 0 && issuer < C::kIssuers) {
             constexpr uint32_t idesc = make_idesc_f16(BT);
             Ring rx, ra;
             bool ok = true;
             int si = 0;   // segment index: selects the accumulator buffer
             for (int u = u_begin; u < u_end && ok; ++si) {
-                const uint32_t d_acc = tmem_base + (uint32_t)((si % C::kAccBufs) * C::kAccCols);
+                const uint32_t d_acc = tmem_base + (uint32_t)((si % C::kAccBufs) * C::kAccCols + issuer * (BT * C::kWT));
                 const int tile = u / total_kb;
                 const int nkb = min(total_kb - (u - tile * total_kb), u_end - u);
                 for (int j = 0; j < nkb; ++j) {
                     ok = mbar_wait(bar_full_a + 8 * ra.stage, ra.phase, s_dead, 4) &&
                          mbar_wait(bar_full_x + 8 * rx.stage, rx.phase, s_dead, 8);
                     if (!ok) break;
-                    TC_TRACE(1, u - u_begin + j, 0);
+                    if (issuer == 0) TC_TRACE(1, u - u_begin + j, 0);
                     tc_fence_after();
                     const uint32_t a_col = tmem_a0 + ra.stage * C::kACols;
                     // one descriptor per K block; the 16-element K steps only add to its start-address field
                     const uint64_t db0 = make_desc_sw128(s_x + rx.stage * C::kXBytes);
+                    constexpr int kSteps = C::kSlabs * 4;              // 16-element K steps per K block
+                    constexpr int kMine = kSteps / C::kIssuers;        // ... of which this issuer takes a contiguous half
 #pragma unroll
-                    for (int sl = 0; sl < C::kSlabs; ++sl) {
-#pragma unroll
-                        for (int kk = 0; kk < 4; ++kk) {
-                            const uint64_t db = db0 + (uint64_t)((sl * (BT * 128) + kk * 32) >> 4);
-                            const uint32_t a_k = a_col + (sl * 4 + kk) * 8;           // 16 K elements = 8 columns
-                            if (sl == 0 && kk == 0) {
-                                const uint32_t acc = j > 0 ? 1u : 0u;                 // first MMA of a segment overwrites
-                                umma_f16_ts(d_acc, a_k, db, idesc, acc);
-                                if (PAIRED) umma_f16_ts(d_acc + BT, a_k + BK / 2, db, idesc, acc);
-                            } else {
-                                umma_f16_ts_acc(d_acc, a_k, db, idesc);
-                                if (PAIRED) umma_f16_ts_acc(d_acc + BT, a_k + BK / 2, db, idesc);
-                            }
+                    for (int t = 0; t < kMine; ++t) {
+                        const int step = issuer * kMine + t;
+                        const int sl = step >> 2, kk = step & 3;
+                        const uint64_t db = db0 + (uint64_t)((sl * (BT * 128) + kk * 32) >> 4);
+                        const uint32_t a_k = a_col + step * 8;             // 16 K elements = 8 columns
+                        if (t == 0) {
+                            const uint32_t acc = j > 0 ? 1u : 0u;              // first MMA of a segment overwrites
+                            umma_f16_ts(d_acc, a_k, db, idesc, acc);
+                            if (PAIRED) umma_f16_ts(d_acc + BT, a_k + BK / 2, db, idesc, acc);
+                        } else {
+                            umma_f16_ts_acc(d_acc, a_k, db, idesc);
+                            if (PAIRED) umma_f16_ts_acc(d_acc + BT, a_k + BK / 2, db, idesc);
                         }
                     }
                     umma_commit(bar_empty_a + 8 * ra.stage);
                     umma_commit(bar_empty_x + 8 * rx.stage);
-                    TC_TRACE(1, u - u_begin + j, 1);
+                    if (issuer == 0) TC_TRACE(1, u - u_begin + j, 1);
                     ra.advance(kNA);
                     rx.advance(kNS);
                 }
@@ -505,7 +511,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 u += nkb;
             }
         }
-    } else {
+    } else if (warp >= 2 && warp <= 9) {
         // ================= dequant warps; after each segment, the epilogue =================
         // A warp may touch only the TMEM lanes of its quarter (warp % 4), so the weight row a thread
         // converts is 32 * (warp % 4) + lane; the two warps of a quarter split the K range of a stage.
@@ -546,6 +552,16 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     float g[8], uu[8];
                     tmem_ld8(t_acc + col, g);
                     if (PAIRED) tmem_ld8(t_acc + BT + col, uu);
+                    if (C::kIssuers == 2) {   // second issuer's half of the K steps, added in fixed order
+                        float g2[8], u2[8];
+                        tmem_ld8(t_acc + BT * C::kWT + col, g2);
+                        if (PAIRED) tmem_ld8(t_acc + BT * C::kWT + BT + col, u2);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            g[j] += g2[j];
+                            if (PAIRED) uu[j] += u2[j];
+                        }
+                    }
                     if (direct) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
