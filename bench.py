@@ -224,7 +224,7 @@ def run_dense(args, world, rank, local, m_list, workload: str) -> dict:
     stack = DenseStack(world, rank, device)
     xs = {M: stack.inputs(M) for M in m_list}
     lib = _cabi.load()
-    use_graphs = (world == 1) and not args.eager
+    use_graphs = not args.eager   # NCCL all-reduce is captured with the GEMMs when world > 1
     side = torch.cuda.Stream(device=device)
 
     def step(i: int):
@@ -388,7 +388,7 @@ def run_moe(args, world, rank, local, m_list=(1, 8, 64, 256)) -> dict:
     layer = par.ExpertParallelMoE(w13, s13, w2, s2, E) if world > 1 else None
     lib = _cabi.load()
     results = []
-    use_graphs = (world == 1) and not args.eager
+    use_graphs = not args.eager   # the all-gather / reduce-scatter EP path is graph-capturable
     side = torch.cuda.Stream(device=device)
     n_sets = 16     # distinct token batches per M, so that consecutive steps route to different experts (L2 cannot hold them)
     for M in m_list:

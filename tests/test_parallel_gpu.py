@@ -1,0 +1,76 @@
+"""Multi-GPU parity (needs >= 2 GPUs, skipped otherwise): tensor-parallel dense layers with NCCL all-reduce and
+expert-parallel MoE (all-gather / reduce-scatter and all-to-all dispatch) against the single-process CPU oracle."""
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    from oracle import linear as olin, moe as omoe
+    from tests.helpers import make_dense, make_moe
+    from vllm_fp8_w8a16_sm70_b200 import ops, parallel as par
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    res = {}
+    try:
+        # ---- dense TP: column-parallel up projection, row-parallel down projection + all-reduce ----
+        x, w1, s1, bh = make_dense(9, 1024, 512, seed=1)
+        _, w2, s2, _ = make_dense(9, 512, 1024, seed=2)
+        wc, sc = par.shard_column_parallel(w1, s1, world, rank)
+        wr, sr = par.shard_row_parallel(w2, s2, world, rank)
+        col = par.TensorParallelLinear(wc.cuda(), sc.cuda(), bh, "column")
+        row = par.TensorParallelLinear(wr.cuda(), sr.cuda(), bh, "row")
+        h = col.forward(x.cuda())
+        y = row.forward(h)
+        h_full = olin.oracle_linear_fp32(x, w1, s1, bh).to(torch.float16)
+        per = 1024 // world
+        st = olin.error_stats(h.cpu(), h_full[:, rank * per:(rank + 1) * per].float())
+        res["tp_col"] = st["rel_rms"] < 1e-2
+        y_ref = olin.oracle_linear_fp32(h_full, w2, s2, bh)
+        st = olin.error_stats(y.cpu(), y_ref)
+        res["tp_row_allreduce"] = st["rel_rms"] < 1.5e-2 and st["finite"]
+        # ---- MoE EP: each rank brings its own tokens ----
+        E, I, H, topk, M = 16, 128, 256, 4, 12
+        base = make_moe(E, I, H, 1, topk, seed=99)
+        d = make_moe(E, I, H, M, topk, seed=10 + rank)
+        per = E // world
+        lo, hi = rank * per, (rank + 1) * per
+        layer = par.ExpertParallelMoE(base["w13"][lo:hi].cuda(), base["s13"][lo:hi].cuda(), base["w2"][lo:hi].cuda(),
+                                      base["s2"][lo:hi].cuda(), E)
+        ref = omoe.moe_reference_fp32(d["x"], d["tw"], d["ids"], base["w13"], base["s13"], base["w2"], base["s2"])
+        for mode in ("allgather", "a2a"):
+            out = layer.forward(d["x"].cuda(), d["tw"].cuda(), d["ids"].cuda(), mode=mode)
+            st = omoe.moe_error_stats(out.cpu(), ref)
+            res[f"ep_{mode}"] = st["cos"] > 0.9999 and st["l2rel"] < 2e-2
+        res["status"] = ops.device_status() == 0
+    finally:
+        q.put((rank, res))
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp_and_ep_on_two_gpus(lib):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    got = dict(q.get(timeout=300) for _ in procs)
+    for p in procs:
+        p.join(60)
+    for r in range(2):
+        assert got[r] and all(got[r].values()), got

@@ -48,6 +48,8 @@ __global__ void __launch_bounds__(kThreads)
 k_gemv(const __half* __restrict__ x, const uint8_t* __restrict__ w, const void* __restrict__ scales, int scale_dtype,
        __half* __restrict__ out, float* __restrict__ partial, unsigned int* __restrict__ tickets, int N, int K,
        int block_h, int Kb, int k_chunk, int splits, int row_groups) {
+    pdl_trigger();   // let the next kernel of the stream begin launching
+    pdl_wait();      // the activations (and the workspace) come from earlier kernels
     const int lane = threadIdx.x & 31;
     const int gwarp = (blockIdx.x * kThreads + threadIdx.x) >> 5;
     const int total_warps = (gridDim.x * kThreads) >> 5;
@@ -236,10 +238,10 @@ int launch_gemv(const __half* x, const uint8_t* w, const void* scales, int scale
         const __half* xm = x + (int64_t)m0 * K;
         __half* om = out + (int64_t)m0 * N;
         switch (mc) {
-            case 1: k_gemv<1><<<grid, kThreads, 0, st>>>(xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
-            case 2: k_gemv<2><<<grid, kThreads, 0, st>>>(xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
-            case 3: k_gemv<3><<<grid, kThreads, 0, st>>>(xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
-            default: k_gemv<4><<<grid, kThreads, 0, st>>>(xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
+            case 1: launch_pdl(k_gemv<1>, dim3(grid), dim3(kThreads), 0, st, xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
+            case 2: launch_pdl(k_gemv<2>, dim3(grid), dim3(kThreads), 0, st, xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
+            case 3: launch_pdl(k_gemv<3>, dim3(grid), dim3(kThreads), 0, st, xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
+            default: launch_pdl(k_gemv<4>, dim3(grid), dim3(kThreads), 0, st, xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
         }
         int rc = check_launch("gemv");
         if (rc) return rc;

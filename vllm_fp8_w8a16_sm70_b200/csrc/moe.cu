@@ -31,6 +31,8 @@ template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16
 template <typename T, int PER_LANE>
 __global__ void __launch_bounds__(128) k_topk_softmax(const T* __restrict__ logits, int M, int E, int topk, int renorm,
                                                       int* __restrict__ ids, float* __restrict__ weights) {
+    pdl_trigger();
+    pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (warp >= M) return;
     const T* row = logits + (int64_t)warp * E;
@@ -116,11 +118,13 @@ __global__ void __launch_bounds__(kAlignThreads)
 k_align(const IdT* __restrict__ ids, int R, const int* __restrict__ expert_map, int n_global, int E, int bt,
         int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ tile_offsets,
         int* __restrict__ sorted_route, int* __restrict__ inv_pos) {
+    pdl_trigger();
     extern __shared__ int sm[];
     int* warp_hist = sm;                       // [kAlignWarps][E] -> later: running placement cursor
     int* s_off = sm + kAlignWarps * E;         // [E + 1]
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     for (int i = tid; i < kAlignWarps * E; i += kAlignThreads) warp_hist[i] = 0;
+    pdl_wait();   // the expert ids come from the previous kernel
     __syncthreads();
 
     // contiguous segment of routes per warp, walked in order 32 at a time
@@ -144,9 +148,29 @@ k_align(const IdT* __restrict__ ids, int R, const int* __restrict__ expert_map, 
         s_off[e] = run;  // counts for now
     }
     __syncthreads();
-    if (tid == 0) {  // E is small (<= 1024): a serial scan is a few microseconds at most
-        int run = 0, trun = 0;
-        for (int e = 0; e < E; ++e) {
+    if (warp == 0) {
+        // exclusive scan of the counts (rows) and of ceil(count / bt) (token tiles) by one warp: every
+        // lane scans a contiguous run of experts, the lane totals are scanned with shuffles
+        const int per_lane = (E + 31) / 32;
+        const int e0 = lane * per_lane, e1 = min(E, e0 + per_lane);
+        int rows = 0, tiles = 0;
+        for (int e = e0; e < e1; ++e) {
+            const int c = s_off[e];
+            rows += c;
+            tiles += (c + bt - 1) / bt;
+        }
+        int rows_incl = rows, tiles_incl = tiles;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int a = __shfl_up_sync(0xFFFFFFFFu, rows_incl, o);
+            const int b = __shfl_up_sync(0xFFFFFFFFu, tiles_incl, o);
+            if (lane >= o) {
+                rows_incl += a;
+                tiles_incl += b;
+            }
+        }
+        int run = rows_incl - rows, trun = tiles_incl - tiles;
+        for (int e = e0; e < e1; ++e) {
             const int c = s_off[e];
             s_off[e] = run;
             offsets[e] = run;
@@ -154,9 +178,11 @@ k_align(const IdT* __restrict__ ids, int R, const int* __restrict__ expert_map, 
             run += c;
             trun += (c + bt - 1) / bt;
         }
-        s_off[E] = run;
-        offsets[E] = run;
-        tile_offsets[E] = trun;
+        if (lane == 31) {
+            s_off[E] = rows_incl;
+            offsets[E] = rows_incl;
+            tile_offsets[E] = tiles_incl;
+        }
     }
     __syncthreads();
     const int n_valid = s_off[E];
@@ -188,6 +214,8 @@ k_align(const IdT* __restrict__ ids, int R, const int* __restrict__ expert_map, 
 __global__ void __launch_bounds__(256)
 k_gather(const __half* __restrict__ x, const int* __restrict__ sorted_route, const float* __restrict__ topk_w, int R,
          int topk, int H, int weight_on_input, __half* __restrict__ x_sorted, float* __restrict__ w_sorted) {
+    pdl_trigger();
+    pdl_wait();
     const int pos = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (pos >= R) return;
     const int route = sorted_route[pos];
@@ -224,6 +252,8 @@ k_gather(const __half* __restrict__ x, const int* __restrict__ sorted_route, con
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 k_combine(const __half* __restrict__ y_sorted, const int* __restrict__ inv_pos, int topk, int H, __half* __restrict__ out) {
+    pdl_trigger();
+    pdl_wait();
     const int token = blockIdx.x;
     extern __shared__ int s_pos[];
     for (int j = threadIdx.x; j < topk; j += blockDim.x) s_pos[j] = inv_pos[(int64_t)token * topk + j];
@@ -257,7 +287,7 @@ template <typename T>
 int launch_topk_t(const T* logits, int M, int E, int topk, int renorm, int* ids, float* weights, cudaStream_t st) {
     const int per_lane = (E + 31) / 32;
     const unsigned blocks = (unsigned)((M + 3) / 4);
-#define W8A16_TOPK(PL) k_topk_softmax<T, PL><<<blocks, 128, 0, st>>>(logits, M, E, topk, renorm, ids, weights)
+#define W8A16_TOPK(PL) launch_pdl(k_topk_softmax<T, PL>, dim3(blocks), dim3(128), 0, st, logits, M, E, topk, renorm, ids, weights)
     if (per_lane <= 1) W8A16_TOPK(1);
     else if (per_lane <= 2) W8A16_TOPK(2);
     else if (per_lane <= 4) W8A16_TOPK(4);
@@ -293,16 +323,16 @@ int launch_align(const void* ids, int ids_are_i64, int R, const int* expert_map,
             W8A16_CUDA(cudaFuncSetAttribute(k_align<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             set64 = true;
         }
-        k_align<long long><<<1, kAlignThreads, smem, st>>>(reinterpret_cast<const long long*>(ids), R, expert_map, n_global, E, bt,
-                                                            counts, offsets, tile_offsets, sorted_route, inv_pos);
+        launch_pdl(k_align<long long>, dim3(1), dim3(kAlignThreads), smem, st, reinterpret_cast<const long long*>(ids), R, expert_map,
+                   n_global, E, bt, counts, offsets, tile_offsets, sorted_route, inv_pos);
     } else {
         static bool set32 = false;
         if (!set32 && smem > 48 * 1024) {
             W8A16_CUDA(cudaFuncSetAttribute(k_align<int>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             set32 = true;
         }
-        k_align<int><<<1, kAlignThreads, smem, st>>>(reinterpret_cast<const int*>(ids), R, expert_map, n_global, E, bt, counts,
-                                                      offsets, tile_offsets, sorted_route, inv_pos);
+        launch_pdl(k_align<int>, dim3(1), dim3(kAlignThreads), smem, st, reinterpret_cast<const int*>(ids), R, expert_map, n_global,
+                   E, bt, counts, offsets, tile_offsets, sorted_route, inv_pos);
     }
     return check_launch("moe_align");
 }
@@ -311,14 +341,14 @@ int launch_gather(const __half* x, const int* sorted_route, const float* topk_w,
                   __half* x_sorted, float* w_sorted, cudaStream_t st) {
     W8A16_REQUIRE(H % 8 == 0, FP8W8A16_ERR_UNSUPPORTED, "moe_gather: hidden size %d must be a multiple of 8", H);
     if (R == 0) return 0;
-    k_gather<<<(unsigned)((R + 7) / 8), 256, 0, st>>>(x, sorted_route, topk_w, R, topk, H, weight_on_input, x_sorted, w_sorted);
+    launch_pdl(k_gather, dim3((unsigned)((R + 7) / 8)), dim3(256), 0, st, x, sorted_route, topk_w, R, topk, H, weight_on_input, x_sorted, w_sorted);
     return check_launch("moe_gather");
 }
 
 int launch_combine(const __half* y_sorted, const int* inv_pos, int M, int topk, int H, __half* out, cudaStream_t st) {
     W8A16_REQUIRE(H % 8 == 0, FP8W8A16_ERR_UNSUPPORTED, "moe_combine: hidden size %d must be a multiple of 8", H);
     if (M == 0) return 0;
-    k_combine<<<(unsigned)M, 256, topk * sizeof(int), st>>>(y_sorted, inv_pos, topk, H, out);
+    launch_pdl(k_combine, dim3((unsigned)M), dim3(256), topk * sizeof(int), st, y_sorted, inv_pos, topk, H, out);
     return check_launch("moe_combine");
 }
 

@@ -114,7 +114,50 @@ class ExpertParallelMoE:
         return ops.moe_forward(rows, ones, local_ids.reshape(-1, 1).contiguous(), self.w13, self.s13, self.w2, self.s2,
                                block_h=self.block_h)
 
-    def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor, mode: str = "auto") -> torch.Tensor:
+        """``mode``: "a2a" = variable-size all-to-all dispatch / combine (one host synchronisation for the split
+        sizes; traffic proportional to the routed rows), "allgather" = fixed-size all-gather of tokens and routes,
+        local experts on every token through ``expert_map``, reduce-scatter of the outputs (no host
+        synchronisation, CUDA-graph capturable; the right choice for decode batches), "auto" = all-gather up to
+        4096 tokens in flight, all-to-all above."""
+        if mode == "auto":
+            mode = "allgather" if x.shape[0] * self.ep_size <= 4096 else "a2a"
+        if mode == "allgather" and self.ep_size > 1 and self._experts == self._engine_experts:
+            return self.forward_allgather(x, topk_weights, topk_ids)
+        return self.forward_a2a(x, topk_weights, topk_ids)
+
+    def forward_allgather(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
+        """Every rank brings M tokens (the same M on all ranks).  all-gather -> [P*M] tokens; this rank's experts
+        contribute to every token (routes to other ranks' experts are dropped by the expert_map, exactly the
+        reference's tolerated-EP semantics, vllm_serve.py:2237-2243); reduce-scatter(sum) returns each rank the
+        finished rows of its own tokens."""
+        P = self.ep_size
+        M, H = x.shape
+        topk = topk_ids.shape[-1]
+        # one collective instead of three: activations, expert ids and route weights of a token travel as one
+        # packed row of bytes (decode-sized exchanges are latency-bound, not bandwidth-bound)
+        ids32 = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
+        row_bytes = 2 * H + 8 * topk
+        packed = torch.empty((M, row_bytes), dtype=torch.uint8, device=x.device)
+        packed[:, :2 * H] = x.contiguous().view(torch.uint8).reshape(M, 2 * H)
+        packed[:, 2 * H:2 * H + 4 * topk] = ids32.contiguous().view(torch.uint8).reshape(M, 4 * topk)
+        packed[:, 2 * H + 4 * topk:] = topk_weights.contiguous().view(torch.uint8).reshape(M, 4 * topk)
+        gathered = torch.empty((P * M, row_bytes), dtype=torch.uint8, device=x.device)
+        dist.all_gather_into_tensor(gathered, packed, group=self.group)
+        xg = gathered[:, :2 * H].contiguous().view(torch.float16).reshape(P * M, H)
+        ig = gathered[:, 2 * H:2 * H + 4 * topk].contiguous().view(torch.int32).reshape(P * M, topk)
+        wg = gathered[:, 2 * H + 4 * topk:].contiguous().view(torch.float32).reshape(P * M, topk)
+        if getattr(self, "_emap", None) is None or self._emap.device != x.device:
+            rank = dist.get_rank(self.group)
+            emap = torch.full((self.num_experts,), -1, dtype=torch.int32)
+            emap[rank * self.local_experts:(rank + 1) * self.local_experts] = torch.arange(self.local_experts, dtype=torch.int32)
+            self._emap = emap.to(x.device)
+        y = ops.moe_forward(xg, wg, ig, self.w13, self.s13, self.w2, self.s2, block_h=self.block_h, expert_map=self._emap)
+        out = x.new_empty((M, H))
+        dist.reduce_scatter_tensor(out, y, op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+    def forward_a2a(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         M, H = x.shape
         topk = topk_ids.shape[-1]
         order, send_counts, local_ids = ep_plan(topk_ids, self.num_experts, self.ep_size)
