@@ -323,7 +323,8 @@ def shape_of(stack, name):
 
 
 def run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, workload) -> dict:
-    """Same sweep through Fp8LinearMethod.apply with pinned HOST activations in and HOST results out every call."""
+    """Same sweep through Fp8LinearMethod.apply with the step's activations copied in from pinned HOST memory and
+    its results copied back to pinned HOST memory inside the timed region."""
     from vllm_fp8_w8a16_sm70_b200 import Fp8LinearMethod
     import types
     method = Fp8LinearMethod((128, 128))
@@ -335,21 +336,31 @@ def run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, wo
             objs[name] = types.SimpleNamespace(weight=lin.w, weight_scale_inv=lin.s, weight_block_size=[128, 128],
                                                input_size_per_partition=lin.K, output_size_per_partition=lin.N, mode=lin.mode)
         layers.append(objs)
-    host_x = {M: {n: torch.randn(M, layers[0][n].input_size_per_partition).to(torch.float16).pin_memory() for n in layers[0]} for M in m_list}
-    host_y = {M: {n: torch.empty(M, layers[0][n].output_size_per_partition, dtype=torch.float16).pin_memory() for n in layers[0]} for M in m_list}
-    h2d = sum(t.numel() * 2 for M in m_list for t in host_x[M].values())
-    d2h = sum(t.numel() * 2 for M in m_list for t in host_y[M].values())
+    # One pinned HOST buffer holds every activation matrix of a step, one holds every result: per step there is
+    # one host->device copy of the inputs, the 4 x len(m_list) apply() calls, one device->host copy of the results.
+    names = list(layers[0])
+    x_shapes = [(M, n, layers[0][n].input_size_per_partition) for M in m_list for n in names]
+    y_shapes = [(M, n, layers[0][n].output_size_per_partition) for M in m_list for n in names]
+    host_x = torch.randn(sum(M * k for M, _, k in x_shapes)).to(torch.float16).pin_memory()
+    host_y = torch.empty(sum(M * k for M, _, k in y_shapes), dtype=torch.float16).pin_memory()
+    dev_x = torch.empty(host_x.shape, dtype=torch.float16, device=device)
+    dev_y = torch.empty(host_y.shape, dtype=torch.float16, device=device)
+    h2d, d2h = host_x.numel() * 2, host_y.numel() * 2
 
     def step(i):
         lay = layers[i % len(layers)]
-        for M in m_list:
-            for name in lay:
-                x = host_x[M][name].to(device, non_blocking=True)
-                y = method.apply(lay[name], x)
-                if lay[name].mode == "row" and world > 1:
-                    import torch.distributed as dist
-                    dist.all_reduce(y)
-                host_y[M][name].copy_(y, non_blocking=True)
+        dev_x.copy_(host_x, non_blocking=True)
+        xo = yo = 0
+        for (M, name, k), (_, _, n) in zip(x_shapes, y_shapes):
+            x = dev_x[xo:xo + M * k].view(M, k)
+            y = method.apply(lay[name], x)
+            if lay[name].mode == "row" and world > 1:
+                import torch.distributed as dist
+                dist.all_reduce(y)
+            dev_y[yo:yo + M * n].view(M, n).copy_(y)
+            xo += M * k
+            yo += M * n
+        host_y.copy_(dev_y, non_blocking=True)
     for i in range(max(1, args.warmup)):
         step(i)
     barrier_sync(world)

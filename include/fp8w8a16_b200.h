@@ -39,6 +39,10 @@ extern "C" {
 #define FP8W8A16_DTYPE_F16 1
 #define FP8W8A16_DTYPE_BF16 2
 
+/* gated activation of the MoE gate/up projection (reference: _moe_activation, vllm_serve.py:1627-1636) */
+#define FP8W8A16_ACT_SILU 1
+#define FP8W8A16_ACT_GELU 2 /* erf form, torch.nn.functional.gelu's default */
+
 /* fp8w8a16_linear `algo` */
 #define FP8W8A16_ALGO_AUTO 0 /* by M, as the reference's _v100_fp8_gemm dispatch does (vllm_serve.py:1032-1100) */
 #define FP8W8A16_ALGO_GEMV 1 /* CUDA-core split-K GEMV, any M (weights re-streamed per 4 tokens) */
@@ -117,7 +121,8 @@ int fp8w8a16_moe_token_tile(int R, int num_local_experts);
 
 /* Grouped expert GEMM over expert-sorted rows:
  *   paired == 0: out[r, n] = (x_sorted[r] . dequant(w[e(r), n])) * row_weight[r]      (row_weight may be NULL)
- *   paired != 0: w is a fused [E, 2N, K] gate/up weight; out[r, n] = silu(gate) * up  (FP16 rounding as the reference)
+ *   paired != 0: w is a fused [E, 2N, K] gate/up weight; out[r, n] = act(gate) * up with act = SiLU (paired = 1,
+ *                FP8W8A16_ACT_SILU) or GELU (paired = 2, FP8W8A16_ACT_GELU); FP16 rounding points as the reference
  * offsets / tile_offsets come from fp8w8a16_moe_align with the same token_tile.
  * Replaces fp8_w8a16_grouped_gemv_coalesced / grouped_routed_gemm_a3 / grouped_tiled_gemm
  * (fp8_dequant.cu:1512, 2813, 3166) and TurboMind's fp8_moe_gemm_sm70_out
@@ -133,13 +138,13 @@ size_t fp8w8a16_moe_grouped_gemm_workspace_bytes(int R, int num_local_experts, i
  *   out[m] = sum_j w[m,j] * down_e( silu(gate_e x[m]) * up_e x[m] ),  e = topk_ids[m,j]
  * x FP16 [M,H]; topk_weights fp32 [M,topk]; w13 [E,2I,H], w2 [E,H,I] E4M3; scales as above with
  * block_h 128 or 1.  weight_on_input: multiply x by the route weight instead of the output
- * (apply_router_weight_on_input, vllm_serve.py:1868).  Steps: align -> gather -> grouped w13 with
+ * (apply_router_weight_on_input, vllm_serve.py:1868); activation: FP8W8A16_ACT_SILU or FP8W8A16_ACT_GELU.  Steps: align -> gather -> grouped w13 with
  * fused SiLU*mul -> grouped w2 with fused route weight -> combine; no host synchronisation. */
 int fp8w8a16_moe_forward(const uint16_t* x, const void* topk_ids, int ids_are_i64, const float* topk_weights,
                          const int32_t* expert_map, int n_global_experts, const uint8_t* w13, const void* s13,
                          const uint8_t* w2, const void* s2, int scale_dtype, uint16_t* out, int M, int topk,
-                         int num_local_experts, int H, int I, int block_h, int weight_on_input, void* workspace,
-                         size_t workspace_bytes, void* stream);
+                         int num_local_experts, int H, int I, int block_h, int weight_on_input, int activation,
+                         void* workspace, size_t workspace_bytes, void* stream);
 size_t fp8w8a16_moe_workspace_bytes(int M, int topk, int num_local_experts, int H, int I);
 
 /* Pieces of the layer, exported so each can be checked on its own. */

@@ -83,12 +83,14 @@ def _dq(w_u8: torch.Tensor, scales, bh: int, bw: int) -> torch.Tensor:
     return torch.from_numpy(out)
 
 
-def silu_mul(gate_up: torch.Tensor, I: int) -> torch.Tensor:
-    return F.silu(gate_up[..., :I]) * gate_up[..., I:]
+def silu_mul(gate_up: torch.Tensor, I: int, activation: str = "silu") -> torch.Tensor:
+    """vllm_serve.py:1627-1636 + :1953-1960: act(gate) * up with act = SiLU or GELU (erf form)."""
+    act = F.silu if activation == "silu" else F.gelu
+    return act(gate_up[..., :I]) * gate_up[..., I:]
 
 
 def moe_reference_fp32(x, topk_w, topk_ids, w13_u8, s13, w2_u8, s2, block_h=128, block_w=128,
-                       experts=None) -> torch.Tensor:
+                       experts=None, activation: str = "silu") -> torch.Tensor:
     """fp32 reference, routed-only output [M,H] fp32.  Ids that are negative or
     >= E contribute zero.  ``experts`` optionally limits dequant to the experts
     actually hit (only a speed-up)."""
@@ -105,7 +107,7 @@ def moe_reference_fp32(x, topk_w, topk_ids, w13_u8, s13, w2_u8, s2, block_h=128,
         w2 = torch.from_numpy(dequant_block_scaled(w2_u8[e].cpu().numpy(), s2[e].cpu(), H, I, block_h, block_w).copy()).float()
         tok, slot = torch.nonzero(ids == e, as_tuple=True)
         gu = x[tok] @ w13.T
-        h = silu_mul(gu, I)
+        h = silu_mul(gu, I, activation)
         y = h @ w2.T
         out.index_add_(0, tok, y * tw[tok, slot].unsqueeze(-1))
     return out

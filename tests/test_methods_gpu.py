@@ -103,6 +103,12 @@ def test_moe_method_apply(lib):
     ref = omoe.moe_reference_fp32(xb.to(torch.float16).cpu(), d["tw"], d["ids"], d["w13"], d["s13"].to(torch.bfloat16), d["w2"], d["s2"], 128)
     st = omoe.moe_error_stats(y.float().cpu(), ref)
     assert st["cos"] > 0.9999 and st["l2rel"] < 2e-2, st
-    lay.activation = "gelu"
+    lay.activation = "gelu"     # reference: _moe_activation serves SiLU and GELU (vllm_serve.py:1627-1636)
+    yg = m.apply(lay, xb, d["tw"].cuda(), d["ids"].cuda(), None)
+    refg = omoe.moe_reference_fp32(xb.to(torch.float16).cpu(), d["tw"], d["ids"], d["w13"], d["s13"].to(torch.bfloat16), d["w2"], d["s2"], 128,
+                                   activation="gelu")
+    st = omoe.moe_error_stats(yg.float().cpu(), refg)
+    assert st["cos"] > 0.9999 and st["l2rel"] < 2e-2, st
+    lay.activation = "relu"
     with pytest.raises(NotImplementedError):
         m.apply(lay, xb, d["tw"].cuda(), d["ids"].cuda(), None)

@@ -17,6 +17,7 @@ ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_DEVICE = -1, -2, -3, 
 SCALE_F16, SCALE_F32 = 0, 1
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 ALGO_AUTO, ALGO_GEMV, ALGO_TC = 0, 1, 2
+ACT_SILU, ACT_GELU = 1, 2
 
 # name -> (restype, argtypes); mirrors include/fp8w8a16_b200.h one to one
 PROTOTYPES = {
@@ -39,7 +40,7 @@ PROTOTYPES = {
                                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "fp8w8a16_moe_grouped_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int, c_int]),
     "fp8w8a16_moe_forward": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-                                     c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                     c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
                                      c_size_t, c_void_p]),
     "fp8w8a16_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "fp8w8a16_moe_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),

@@ -1,6 +1,7 @@
 // C-ABI entry points (include/fp8w8a16_b200.h): argument validation, algorithm choice, workspace
 // carve-up and kernel launches.  No allocation, no host synchronisation (except device_status).
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <atomic>
@@ -67,6 +68,19 @@ size_t tc_dense_workspace_bytes(int M, int N, int K) {
     (void)N;
     (void)K;
     return tc_workspace_bytes(tc_pick_bt(M), false);
+}
+
+// Largest token count served by the CUDA-core GEMV under ALGO_AUTO (the reference has the same kind of
+// knob, _COALESCED_GEMV_M_MAX, src/fp8_w8a16_sm70/vllm_serve.py:1063-1072).  Default 1: measured on B200 the
+// tensor-core kernel is faster from two tokens on.  FP8W8A16_GEMV_MAX_M=0..4 overrides it.
+int gemv_max_m() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("FP8W8A16_GEMV_MAX_M");
+        int x = e ? atoi(e) : 1;
+        v = x < 0 ? 0 : (x > 4 ? 4 : x);
+    }
+    return v;
 }
 
 int check_common(const void* x, const void* w, const void* scales, const void* out, int M, int N, int K, int block_h,
@@ -156,6 +170,7 @@ int grouped_gemm(const __half* x_sorted, const uint8_t* w, const void* scales, i
     L.p.out = out;
     L.p.ldo = N;
     L.p.row_weight = row_weight;
+    L.p.activation = paired;
     L.p.n_token_tiles = 0;
     L.p.no_split = tiles_ub > (int64_t)tc_max_tiles_with_tickets() ? 1 : 0;
     L.p.tickets = reinterpret_cast<unsigned int*>(workspace);
@@ -265,7 +280,7 @@ int fp8w8a16_linear(const uint16_t* x, const uint8_t* w, const void* scales, int
     const __half* xh = reinterpret_cast<const __half*>(x);
     __half* oh = reinterpret_cast<__half*>(out);
     cudaStream_t st = (cudaStream_t)stream;
-    if (algo == FP8W8A16_ALGO_AUTO) algo = (M == 1) ? FP8W8A16_ALGO_GEMV : FP8W8A16_ALGO_TC;
+    if (algo == FP8W8A16_ALGO_AUTO) algo = (M <= gemv_max_m()) ? FP8W8A16_ALGO_GEMV : FP8W8A16_ALGO_TC;
     switch (algo) {
         case FP8W8A16_ALGO_GEMV:
             return launch_gemv(xh, w, scales, scale_dtype, oh, M, N, K, block_h, block_w, workspace, workspace_bytes, st);
@@ -316,6 +331,7 @@ int fp8w8a16_moe_grouped_gemm(const uint16_t* x_sorted, const uint8_t* w, const 
     W8A16_REQUIRE(token_tile == 16 || token_tile == 32 || token_tile == 64 || token_tile == 128 || token_tile == 256,
                   FP8W8A16_ERR_INVALID, "moe_grouped_gemm: token_tile=%d not in {16,32,64,128,256}", token_tile);
     W8A16_REQUIRE(R == 0 || (offsets && tile_offsets), FP8W8A16_ERR_INVALID, "moe_grouped_gemm: null route table");
+    W8A16_REQUIRE(paired >= 0 && paired <= 2, FP8W8A16_ERR_INVALID, "moe_grouped_gemm: paired=%d not in {0,1,2}", paired);
     return grouped_gemm(reinterpret_cast<const __half*>(x_sorted), w, scales, scale_dtype, reinterpret_cast<__half*>(out),
                         row_weight, offsets, tile_offsets, R, num_local_experts, N, K, block_h, paired, token_tile, workspace,
                         workspace_bytes, (cudaStream_t)stream);
@@ -346,8 +362,8 @@ size_t fp8w8a16_moe_workspace_bytes(int M, int topk, int num_local_experts, int 
 int fp8w8a16_moe_forward(const uint16_t* x, const void* topk_ids, int ids_are_i64, const float* topk_weights,
                          const int32_t* expert_map, int n_global_experts, const uint8_t* w13, const void* s13,
                          const uint8_t* w2, const void* s2, int scale_dtype, uint16_t* out, int M, int topk,
-                         int num_local_experts, int H, int I, int block_h, int weight_on_input, void* workspace,
-                         size_t workspace_bytes, void* stream) {
+                         int num_local_experts, int H, int I, int block_h, int weight_on_input, int activation,
+                         void* workspace, size_t workspace_bytes, void* stream) {
     W8A16_REQUIRE(M >= 0 && topk >= 1 && num_local_experts >= 1 && H > 0 && I > 0, FP8W8A16_ERR_INVALID,
                   "moe_forward: M=%d topk=%d E=%d H=%d I=%d", M, topk, num_local_experts, H, I);
     if (M == 0) return 0;
@@ -356,6 +372,8 @@ int fp8w8a16_moe_forward(const uint16_t* x, const void* topk_ids, int ids_are_i6
     W8A16_REQUIRE(H % 16 == 0 && I % 16 == 0, FP8W8A16_ERR_UNSUPPORTED,
                   "moe_forward: hidden %d and intermediate %d must be multiples of 16", H, I);
     W8A16_REQUIRE(block_h >= 1, FP8W8A16_ERR_INVALID, "moe_forward: block_h=%d", block_h);
+    W8A16_REQUIRE(activation == FP8W8A16_ACT_SILU || activation == FP8W8A16_ACT_GELU, FP8W8A16_ERR_UNSUPPORTED,
+                  "moe_forward: activation %d is not SiLU (1) or GELU (2)", activation);
     W8A16_REQUIRE((int64_t)M * topk < (1ll << 30), FP8W8A16_ERR_UNSUPPORTED, "moe_forward: too many routed rows");
     const int E = num_local_experts, R = M * topk;
     const MoeLayout L = moe_layout(M, topk, E, H, I);
@@ -381,7 +399,7 @@ int fp8w8a16_moe_forward(const uint16_t* x, const void* topk_ids, int ids_are_i6
     rc = launch_gather(reinterpret_cast<const __half*>(x), sorted_route, topk_weights, R, topk, H, weight_on_input, x_sorted,
                        w_sorted, st);
     if (rc) return rc;
-    rc = grouped_gemm(x_sorted, w13, s13, scale_dtype, h_sorted, nullptr, offsets, tile_offsets, R, E, I, H, block_h, 1, L.bt,
+    rc = grouped_gemm(x_sorted, w13, s13, scale_dtype, h_sorted, nullptr, offsets, tile_offsets, R, E, I, H, block_h, activation, L.bt,
                       ws + L.gemm_ws, L.gemm_ws_bytes, st);
     if (rc) return rc;
     rc = grouped_gemm(h_sorted, w2, s2, scale_dtype, y_sorted, w_sorted, offsets, tile_offsets, R, E, H, I, block_h, 0, L.bt,

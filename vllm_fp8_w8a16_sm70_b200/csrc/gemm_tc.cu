@@ -259,6 +259,7 @@ struct Ring {
 };
 
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
 
 // One output element.  `row` is the row of the activation matrix (expert-sorted row in grouped
 // mode), `n` the output feature.  Rounding points follow the reference's grouped path
@@ -269,7 +270,8 @@ __device__ __forceinline__ void store_out(const TcParams& p, int row, int n, flo
     __half r;
     if (PAIRED) {
         const __half g16 = __float2half_rn(g), u16 = __float2half_rn(u);
-        const __half a16 = __float2half_rn(silu_f(__half2float(g16)));
+        const float gf = __half2float(g16);
+        const __half a16 = __float2half_rn(p.activation == 2 ? gelu_erf_f(gf) : silu_f(gf));
         r = __float2half_rn(__half2float(a16) * __half2float(u16));
     } else {
         r = __float2half_rn(g);

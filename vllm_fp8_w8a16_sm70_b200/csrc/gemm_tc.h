@@ -28,6 +28,7 @@ struct TcParams {
     __half* out;                 // out[row * ldo + n]
     int64_t ldo;
     const float* row_weight;     // optional per-row multiplier (route weight), applied as FP16
+    int activation;              // paired mode: 1 = SiLU(gate) * up, 2 = GELU(gate) * up (erf form)
     // persistent stream-K work split
     int n_token_tiles;           // dense: ceil(M / BT); grouped: read from tile_offsets[E] on the device
     int no_split;                // 1: every CTA takes whole tiles only (no partial tiles, no tickets)

@@ -22,12 +22,15 @@ from .backend import select_backend
 from .linear_method import _check_scale_range, _set
 
 
-def _activation_is_silu(layer) -> bool:
+def _activation_name(layer) -> str:
+    """SiLU / SwiGLU or GELU, as the reference's ``_moe_activation`` (vllm_serve.py:1627-1636); anything else raises."""
     activation = getattr(layer, "activation", "silu")
     name = getattr(activation, "name", str(activation)).upper()
     if "SILU" in name or "SWIGLU" in name:
-        return True
-    raise NotImplementedError(f"FP8 W8A16 MoE engine: unsupported activation {activation!r} (SiLU only)")
+        return "silu"
+    if "GELU" in name:
+        return "gelu"
+    raise NotImplementedError(f"FP8 W8A16 MoE engine: unsupported activation {activation!r}")
 
 
 class Fp8MoEMethod:
@@ -73,7 +76,7 @@ class Fp8MoEMethod:
         """Accepts both the 5-argument form the reference targets (vllm_serve.py:2683) and the
         6-argument form of newer vLLM; the shared-expert arguments are ignored on purpose."""
         del shared_experts_input, shared_experts
-        _activation_is_silu(layer)
+        act = _activation_name(layer)
         x_work = x if x.dtype == torch.float16 else x.to(torch.float16)
         x_work = x_work.contiguous()
         tw = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
@@ -84,7 +87,7 @@ class Fp8MoEMethod:
         out = ops.moe_forward(
             x_work, tw.contiguous(), ids.contiguous(), layer.w13_weight, getattr(layer, f"w13_{self.weight_scale_name}"),
             layer.w2_weight, getattr(layer, f"w2_{self.weight_scale_name}"), block_h=self.block_h, expert_map=emap,
-            weight_on_input=bool(getattr(layer, "apply_router_weight_on_input", False)))
+            weight_on_input=bool(getattr(layer, "apply_router_weight_on_input", False)), activation=act)
         return out if out.dtype == x.dtype else out.to(x.dtype)
 
 

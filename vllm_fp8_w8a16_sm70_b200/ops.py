@@ -17,6 +17,7 @@ from . import _cabi
 from ._cabi import ALGO_AUTO, ALGO_GEMV, ALGO_TC, SCALE_F16, SCALE_F32  # noqa: F401
 
 _WORKSPACES: dict = {}
+_LINEAR_WS_BYTES: dict = {}
 _TICKET_BYTES = 65536
 
 
@@ -52,10 +53,10 @@ def _scale_dtype(s: torch.Tensor) -> int:
     raise RuntimeError(f"scales must be float16 or float32 (got {s.dtype}); cast bf16 scales at load")
 
 
-def workspace(dev: torch.device, nbytes: int) -> torch.Tensor:
+def workspace(dev: torch.device, nbytes: int, stream: Optional[int] = None) -> torch.Tensor:
     """Per (device, stream) scratch buffer.  The first 64 KiB hold the kernels' hand-off counters:
     zero when allocated, left at zero by every kernel.  Grows on demand (a new zeroed buffer)."""
-    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream(dev))
+    key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream(dev) if stream is None else stream)
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < nbytes:
         size = max(int(nbytes), 1 << 20)
@@ -159,10 +160,15 @@ def w8a16_linear(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, N: int,
         out = torch.empty((M, N), dtype=torch.float16, device=dev)
     lib = _cabi.load()
     with _dev_guard(dev):
-        ws = workspace(dev, lib.fp8w8a16_linear_workspace_bytes(M, N, K))
-        _cabi.check(lib.fp8w8a16_linear(x.data_ptr(), w.data_ptr(), scales.data_ptr(), _scale_dtype(scales), out.data_ptr(),
-                                        M, N, K, block_h, block_w, algo, ws.data_ptr(), ws.numel(), _stream(dev)),
-                    "fp8w8a16_linear")
+        st = _stream(dev)
+        need = _LINEAR_WS_BYTES.get((M, N, K))
+        if need is None:
+            need = _LINEAR_WS_BYTES[(M, N, K)] = lib.fp8w8a16_linear_workspace_bytes(M, N, K)
+        ws = workspace(dev, need, st)
+        rc = lib.fp8w8a16_linear(x.data_ptr(), w.data_ptr(), scales.data_ptr(), _scale_dtype(scales), out.data_ptr(),
+                                 M, N, K, block_h, block_w, algo, ws.data_ptr(), ws.numel(), st)
+        if rc:
+            _cabi.check(rc, "fp8w8a16_linear")
     return out
 
 
@@ -290,15 +296,20 @@ def moe_grouped_gemm(x_sorted: torch.Tensor, w: torch.Tensor, scales: torch.Tens
     return out
 
 
+_ACTIVATIONS = {"silu": _cabi.ACT_SILU, "gelu": _cabi.ACT_GELU}
+
+
 def moe_forward(x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor, w13: torch.Tensor, s13: torch.Tensor,
                 w2: torch.Tensor, s2: torch.Tensor, block_h: int = 128, expert_map: Optional[torch.Tensor] = None,
-                weight_on_input: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                weight_on_input: bool = False, out: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
     """Routed-only MoE layer output float16 [M, H] (reference: ``_our_moe_apply``,
     src/fp8_w8a16_sm70/vllm_serve.py:2175-2411)."""
     w13, w2 = _as_u8(w13), _as_u8(w2)
     dev = _require_cuda(x, topk_weights, topk_ids, w13, s13, w2, s2)
     if x.dtype != torch.float16:
         raise RuntimeError("x must be float16")
+    if activation not in _ACTIVATIONS:
+        raise NotImplementedError(f"unsupported MoE activation {activation!r} (silu or gelu)")
     if topk_weights.dtype != torch.float32:
         raise RuntimeError("topk_weights must be float32")
     if topk_ids.dtype not in (torch.int32, torch.int64):
@@ -330,7 +341,8 @@ def moe_forward(x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Ten
         _cabi.check(lib.fp8w8a16_moe_forward(x.data_ptr(), topk_ids.data_ptr(), 1 if topk_ids.dtype == torch.int64 else 0,
                                              topk_weights.data_ptr(), emap_ptr, n_global, w13.data_ptr(), s13.data_ptr(),
                                              w2.data_ptr(), s2.data_ptr(), _scale_dtype(s13), out.data_ptr(), M, topk, E, H, I,
-                                             block_h, 1 if weight_on_input else 0, ws.data_ptr(), ws.numel(), _stream(dev)),
+                                             block_h, 1 if weight_on_input else 0, _ACTIVATIONS[activation], ws.data_ptr(), ws.numel(),
+                                             _stream(dev)),
                     "fp8w8a16_moe_forward")
     return out
 
