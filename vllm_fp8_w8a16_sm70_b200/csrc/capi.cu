@@ -64,10 +64,24 @@ namespace {
 
 inline size_t align_up(size_t v, size_t a) { return (v + a - 1) / a * a; }
 
+int dense_token_tile(int M);
+
 size_t tc_dense_workspace_bytes(int M, int N, int K) {
     (void)N;
     (void)K;
-    return tc_workspace_bytes(tc_pick_bt(M), false);
+    return tc_workspace_bytes(dense_token_tile(M), false);
+}
+
+// Token tile of the tensor-core GEMM for a dense problem of M tokens.  Above 128 tokens the tile is 256
+// (FP8W8A16_PREFILL_BT=128 selects the 128-token tile with double-buffered accumulators instead).
+int dense_token_tile(int M) {
+    static int prefill_bt = -1;
+    if (prefill_bt < 0) {
+        const char* e = getenv("FP8W8A16_PREFILL_BT");
+        prefill_bt = (e && atoi(e) == 128) ? 128 : 256;
+    }
+    const int bt = tc_pick_bt(M);
+    return bt > 128 ? prefill_bt : bt;
 }
 
 // Largest token count served by the CUDA-core GEMV under ALGO_AUTO (the reference has the same kind of
@@ -99,7 +113,7 @@ int check_common(const void* x, const void* w, const void* scales, const void* o
 
 int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_dtype, __half* out, int M, int N, int K,
               int block_h, void* workspace, size_t workspace_bytes, cudaStream_t st) {
-    const int bt = tc_pick_bt(M), bk = tc_block_k(bt, false);
+    const int bt = dense_token_tile(M), bk = tc_block_k(bt, false);
     const int token_tiles = (M + bt - 1) / bt;
     const int64_t tiles = (int64_t)((N + 127) / 128) * token_tiles;
     const size_t need = tc_workspace_bytes(bt, false);

@@ -296,9 +296,18 @@ struct Seg {
 
 template <int BT>
 __device__ __forceinline__ void get_seg(const TcParams& p, int u, int u_end, int total_kb, int n_tt, int units_per_cta, Seg& s) {
-    s.tile = u / total_kb;
-    s.kb0 = u - s.tile * total_kb;
+    const int v = u / total_kb;
+    s.kb0 = u - v * total_kb;
     s.nkb = min(total_kb - s.kb0, u_end - u);
+    if (p.no_split) {
+        // whole tiles, dealt round-robin: at any moment the CTAs work on gridDim.x consecutive tiles (token tiles
+        // fastest), so a weight slab is in flight for all its token tiles at once and is read from HBM once
+        const int per_cta = units_per_cta / total_kb;
+        const int c = v / per_cta;
+        s.tile = (v - c * per_cta) * (int)gridDim.x + c;
+    } else {
+        s.tile = v;
+    }
     s.slab = s.tile / n_tt;             // token tiles fastest: concurrently running CTAs share a weight slab
     const int tt = s.tile - s.slab * n_tt;
     s.expert = 0;
@@ -315,8 +324,13 @@ __device__ __forceinline__ void get_seg(const TcParams& p, int u, int u_end, int
         s.row_begin = tt * BT;
         s.rows_valid = min(BT, p.M - s.row_begin);
     }
-    s.first_c = (s.tile * total_kb) / units_per_cta;
-    s.n_contrib = ((s.tile + 1) * total_kb - 1) / units_per_cta - s.first_c + 1;
+    if (p.no_split) {
+        s.first_c = 0;
+        s.n_contrib = 1;
+    } else {
+        s.first_c = (s.tile * total_kb) / units_per_cta;
+        s.n_contrib = ((s.tile + 1) * total_kb - 1) / units_per_cta - s.first_c + 1;
+    }
 }
 
 // Workspace slot of contributor `c` for `tile`: slot 0 if the tile is the first one the CTA touches,
@@ -391,11 +405,19 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     const int cta = blockIdx.x;
     int n_tt = p.n_token_tiles, total_units = 0, units_per_cta = 0, u_begin = 0, u_end = 0;
     auto set_range = [&]() {
-        total_units = n_tt * n_slabs * total_kb;
-        units_per_cta = (total_units + (int)gridDim.x - 1) / (int)gridDim.x;
-        if (p.no_split) units_per_cta = (units_per_cta + total_kb - 1) / total_kb * total_kb;  // whole tiles only
-        u_begin = cta * units_per_cta;
-        u_end = min(total_units, u_begin + units_per_cta);
+        const int total_tiles = n_tt * n_slabs;
+        total_units = total_tiles * total_kb;
+        if (p.no_split) {
+            // whole tiles only, tile = cta + i * gridDim.x (see get_seg); units index a per-CTA virtual range
+            units_per_cta = (total_tiles + (int)gridDim.x - 1) / (int)gridDim.x * total_kb;
+            const int mine = cta < total_tiles ? (total_tiles - cta + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+            u_begin = cta * units_per_cta;
+            u_end = u_begin + mine * total_kb;
+        } else {
+            units_per_cta = (total_units + (int)gridDim.x - 1) / (int)gridDim.x;
+            u_begin = cta * units_per_cta;
+            u_end = min(total_units, u_begin + units_per_cta);
+        }
     };
     if (!grouped) set_range();
 
