@@ -92,13 +92,26 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
         : "memory");
     return ok;
 }
+// Same, but the thread may be suspended by the hardware for up to `ns` while the phase is pending: a
+// waiting warp then costs no issue slots (the converting warps need them), and is woken when the phase flips.
+__device__ __forceinline__ uint32_t mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(ns)
+        : "memory");
+    return ok;
+}
 
 // Bounded wait.  Returns false when the CTA has been declared dead (by this or another thread).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* dead, int code) {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer_ns();
     uint32_t spins = 0;
-    while (!mbar_try_wait(bar, parity)) {
+    while (!mbar_try_wait_suspend(bar, parity, 2000u)) {
         if ((++spins & 0x3Fu) == 0u) {
             if (*dead) return false;
             if (globaltimer_ns() - t0 > kTimeoutNs) {
