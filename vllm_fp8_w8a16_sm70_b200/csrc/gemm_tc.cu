@@ -616,34 +616,50 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             tc_fence_before();
             // Hand-off.  All 256 threads take both barriers in every segment, whatever happened above,
             // and act only on values that thread 0 publishes between them, so that a timed-out wait
-            // somewhere in the CTA can never strand part of it at a barrier.
-            if (!direct) __threadfence();
+            // somewhere in the CTA can never strand part of it at a barrier.  Memory ordering: the
+            // partial stores of all threads are ordered before the first barrier (CTA scope); thread 0's
+            // fence + ticket increment publishes them device-wide (release, cumulative), and its fence
+            // after the increment makes the other contributors' partials visible to every thread that
+            // passes the second barrier (acquire).
             epi_bar_sync();
             if (td == 0) {
                 const int dead = *s_dead;
-                s_ticket[0] = (!direct && !dead) ? (int)atomicAdd(&p.tickets[sg.tile], 1u) : -1;
+                int tk = -1;
+                if (!direct && !dead) {
+                    __threadfence();
+                    tk = (int)atomicAdd(&p.tickets[sg.tile], 1u);
+                    __threadfence();
+                }
+                s_ticket[0] = tk;
                 s_ticket[1] = dead;
             }
             epi_bar_sync();
             const int ticket = s_ticket[0];
             const int dead_now = s_ticket[1];
             if (!direct && ticket == sg.n_contrib - 1) {
-                __threadfence();
-                // four consecutive output features per thread and step; the contributors' slots are read
-                // with independent 16-byte loads (several in flight) and added in ascending CTA order
+                // Last contributor: add the partial tiles in ascending CTA order (deterministic).  Four
+                // consecutive output features per thread and step; the slots are read eight at a time with
+                // independent 16-byte loads so that one L2 round trip covers eight contributors.
                 for (int idx4 = td; idx4 < BT * 32; idx4 += kDequantThreads) {
                     const int ml = idx4 >> 5, nl = (idx4 & 31) * 4;
                     if (ml >= sg.rows_valid || n0 + nl >= p.N) continue;
                     float4 g = make_float4(0.f, 0.f, 0.f, 0.f), uu = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-                    for (int cc = sg.first_c; cc < sg.first_c + sg.n_contrib; ++cc) {
-                        const float4* ps = reinterpret_cast<const float4*>(
-                            p.partial + (int64_t)partial_slot(cc, sg.tile, total_kb, units_per_cta) * kTileFloats);
-                        const float4 a = __ldcg(&ps[idx4]);
-                        g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
-                        if (PAIRED) {
-                            const float4 b = __ldcg(&ps[BT * 32 + idx4]);
-                            uu.x += b.x; uu.y += b.y; uu.z += b.z; uu.w += b.w;
+                    for (int c0 = 0; c0 < sg.n_contrib; c0 += 8) {
+                        float4 a[8], b[8];
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) {
+                            const int cc = sg.first_c + min(c0 + t, sg.n_contrib - 1);   // clamped: extra loads are ignored below
+                            const float4* ps = reinterpret_cast<const float4*>(
+                                p.partial + (int64_t)partial_slot(cc, sg.tile, total_kb, units_per_cta) * kTileFloats);
+                            a[t] = __ldcg(&ps[idx4]);
+                            if (PAIRED) b[t] = __ldcg(&ps[BT * 32 + idx4]);
+                        }
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) {
+                            if (c0 + t < sg.n_contrib) {
+                                g.x += a[t].x; g.y += a[t].y; g.z += a[t].z; g.w += a[t].w;
+                                if (PAIRED) { uu.x += b[t].x; uu.y += b[t].y; uu.z += b[t].z; uu.w += b[t].w; }
+                            }
                         }
                     }
                     const int row = sg.row_begin + ml, n = n0 + nl;
