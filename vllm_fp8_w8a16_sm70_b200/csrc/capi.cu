@@ -144,6 +144,8 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
     L.w_total_rows = N;
     L.max_units = tiles * ((K + bk - 1) / bk);
     W8A16_REQUIRE(L.max_units < (1ll << 31), FP8W8A16_ERR_UNSUPPORTED, "linear: problem too large for 32-bit work indices");
+    L.p.cluster_size = tc_cluster_size(tiles, (K + bk - 1) / bk, bt, false);
+    L.cluster_tiles = tiles;
     return tc_launch(L, bt, false, st);
 }
 
@@ -194,6 +196,8 @@ int grouped_gemm(const __half* x_sorted, const uint8_t* w, const void* scales, i
     L.w_total_rows = (int64_t)E * rows_w;
     L.max_units = tiles_ub * ((K + bk - 1) / bk);
     W8A16_REQUIRE(L.max_units < (1ll << 31), FP8W8A16_ERR_UNSUPPORTED, "moe_grouped_gemm: problem too large for 32-bit work indices");
+    L.p.cluster_size = tc_cluster_size(tiles_ub, (K + bk - 1) / bk, bt, paired != 0);
+    L.cluster_tiles = tiles_ub;
     return tc_launch(L, bt, paired != 0, st);
 }
 

@@ -33,6 +33,8 @@
 // (fp8_dequant.cu:2029-2031) and TurboMind's __hmul dequant (kernels/gemm/transform.h:151-156).
 #include <cuda.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 #include <unordered_map>
 
@@ -221,6 +223,23 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
 }
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
+// Thread-block cluster helpers (synchronous split-K): every thread of every CTA of the cluster arrives and waits.
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+}
+// Address of the same shared-memory location in the CTA of rank `rank` of this cluster.
+__device__ __forceinline__ uint32_t cluster_map(uint32_t local_saddr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_saddr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+    return v;
+}
+
 // ---- compile-time configuration ------------------------------------------------------------------
 // TMEM columns of one CTA: kAccBufs accumulator buffers of kAccCols fp32 columns (BT per weight
 // tile; two buffers where they fit, so the epilogue of one segment overlaps the MMAs of the next),
@@ -257,6 +276,8 @@ struct TcCfg {
     static_assert(kNS >= 2, "not enough shared memory for a 2-stage TMA ring");
     static_assert(kNA >= 2, "not enough TMEM for two dequantised stages");
     static_assert(kTmemCols * kCtasPerSm <= 512, "co-resident CTAs exceed TMEM");
+    // cluster split-K parks the fp32 partial tile in the (by then idle) raw-tile ring
+    static constexpr bool kClusterOk = kWT * BT * 128 * 4 <= kNS * kRawBytes;
 };
 
 // ring position: stage index and the parity of the current pass over the ring
@@ -420,7 +441,16 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     auto set_range = [&]() {
         const int total_tiles = n_tt * n_slabs;
         total_units = total_tiles * total_kb;
-        if (p.no_split) {
+        if (p.cluster_size > 1) {
+            // synchronous split-K: cluster = tile, rank in cluster = K range (every rank gets at least one block)
+            const int S = p.cluster_size;
+            const int tile = cta / S, rnk = cta - tile * S;
+            const int per = (total_kb + S - 1) / S;
+            units_per_cta = per;
+            const int b = min(total_kb, rnk * per), e = min(total_kb, b + per);
+            u_begin = tile < total_tiles ? tile * total_kb + b : 0;
+            u_end = tile < total_tiles ? tile * total_kb + e : 0;
+        } else if (p.no_split) {
             // whole tiles only, tile = cta + i * gridDim.x (see get_seg); units index a per-CTA virtual range
             units_per_cta = (total_tiles + (int)gridDim.x - 1) / (int)gridDim.x * total_kb;
             const int mine = cta < total_tiles ? (total_tiles - cta + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -578,11 +608,14 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             const uint32_t t_acc = t_lane + (uint32_t)((si % C::kAccBufs) * C::kAccCols);
             if (ok) ok = mbar_wait(bar_acc + 8 * (si % C::kAccBufs), (uint32_t)(si / C::kAccBufs) & 1u, s_dead, 64);
             ok = __all_sync(0xFFFFFFFFu, ok) != 0;  // tcgen05.ld is warp-collective: keep the warp together
-            const bool direct = (sg.n_contrib == 1);
+            const bool clustered = p.cluster_size > 1;
+            const bool direct = !clustered && (sg.n_contrib == 1);
             if (ok) {
                 tc_fence_after();
                 const int n = n0 + n_local;
-                float* part = p.partial + (int64_t)partial_slot(cta, sg.tile, total_kb, units_per_cta) * kTileFloats;
+                // partial tile: a workspace slot (stream-K), or this CTA's idle raw-tile ring (cluster split-K)
+                float* part = clustered ? reinterpret_cast<float*>(smem_dyn + (s_raw - dyn_base))
+                                        : p.partial + (int64_t)partial_slot(cta, sg.tile, total_kb, units_per_cta) * kTileFloats;
 #pragma unroll 1
                 for (int c0 = 0; c0 < kColsPerWarp; c0 += 8) {
                     const int col = hk * kColsPerWarp + c0;
@@ -604,6 +637,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         for (int j = 0; j < 8; ++j)
                             if (col + j < sg.rows_valid && n < p.N)
                                 store_out<PAIRED>(p, sg.row_begin + col + j, n, g[j], PAIRED ? uu[j] : 0.f);
+                    } else if (clustered) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            part[(col + j) * 128 + n_local] = g[j];
+                            if (PAIRED) part[(BT + col + j) * 128 + n_local] = uu[j];
+                        }
                     } else {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -625,7 +664,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (td == 0) {
                 const int dead = *s_dead;
                 int tk = -1;
-                if (!direct && !dead) {
+                if (!direct && !clustered && !dead) {
                     __threadfence();
                     tk = (int)atomicAdd(&p.tickets[sg.tile], 1u);
                     __threadfence();
@@ -636,7 +675,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             epi_bar_sync();
             const int ticket = s_ticket[0];
             const int dead_now = s_ticket[1];
-            if (!direct && ticket == sg.n_contrib - 1) {
+            if (!direct && !clustered && ticket == sg.n_contrib - 1) {
                 // Last contributor: add the partial tiles in ascending CTA order (deterministic).  Four
                 // consecutive output features per thread and step; the slots are read eight at a time with
                 // independent 16-byte loads so that one L2 round trip covers eight contributors.
@@ -767,12 +806,52 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 if (stop) break;
             }
         }
-        if (!stop && pend_i >= 0) epilogue(pend, pend_i);
+        if (!stop && pend_i >= 0) stop = epilogue(pend, pend_i);
+        if (p.cluster_size > 1) {
+            // every CTA of the cluster has parked its fp32 partial tile in its own shared memory
+            cluster_sync_all();
+            if (!stop) {
+                Seg last_sg;   // the one segment of this CTA
+                get_seg<BT>(p, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
+                const int S = p.cluster_size;
+                uint32_t rnk;
+                asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rnk));
+                const int n0 = last_sg.slab * 128;
+                const int chunk = (BT * 32 + S - 1) / S;             // 16-byte groups of the tile reduced by each rank
+                const int lo = (int)rnk * chunk, hi = min(BT * 32, lo + chunk);
+                const uint32_t local_part = s_raw;
+                for (int idx4 = lo + td; idx4 < hi; idx4 += kDequantThreads) {
+                    const int ml = idx4 >> 5, nl = (idx4 & 31) * 4;
+                    if (ml >= last_sg.rows_valid || n0 + nl >= p.N) continue;
+                    float4 g = make_float4(0.f, 0.f, 0.f, 0.f), uu = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+                    for (int t = 0; t < S; ++t) {                        // ascending rank = ascending K: deterministic
+                        const uint32_t peer = cluster_map(local_part, (uint32_t)t);
+                        const float4 a = ld_cluster_f4(peer + (uint32_t)idx4 * 16u);
+                        g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
+                        if (PAIRED) {
+                            const float4 b = ld_cluster_f4(peer + (uint32_t)(BT * 32 + idx4) * 16u);
+                            uu.x += b.x; uu.y += b.y; uu.z += b.z; uu.w += b.w;
+                        }
+                    }
+                    const int row = last_sg.row_begin + ml, n = n0 + nl;
+                    store_out<PAIRED>(p, row, n, g.x, uu.x);
+                    if (n + 1 < p.N) store_out<PAIRED>(p, row, n + 1, g.y, uu.y);
+                    if (n + 2 < p.N) store_out<PAIRED>(p, row, n + 2, g.z, uu.z);
+                    if (n + 3 < p.N) store_out<PAIRED>(p, row, n + 3, g.w, uu.w);
+                }
+            }
+            cluster_sync_all();   // nobody leaves (and frees its shared memory) while a peer may still read it
+        }
     }
 
 #ifdef W8A16_TC_TRACE
     if (threadIdx.x == 64 && blockIdx.x < 512) g_tc_cta[blockIdx.x][2] = globaltimer_ns_raw();
 #endif
+    if (p.cluster_size > 1 && !(has_work && warp >= 2 && warp <= 9)) {
+        cluster_sync_all();   // the dequant warps of a working CTA take these two inside their branch
+        cluster_sync_all();
+    }
     // ---- teardown: every thread arrives here, also after a timed-out wait ----
     if (*s_dead) {
         // let copies and MMAs that are still in flight land before shared memory and TMEM go away
@@ -869,6 +948,7 @@ int launch_cfg(const TcLaunch& L, cudaStream_t st) {
     W8A16_CUDA(cudaGetDevice(&dev));
     if (dev < 64 && !attr_set[dev]) {
         W8A16_CUDA(cudaFuncSetAttribute(k_gemm_tc<BT, BK, PAIRED>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        W8A16_CUDA(cudaFuncSetAttribute(k_gemm_tc<BT, BK, PAIRED>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         attr_set[dev] = true;
     }
     CUtensorMap map_w, map_x;
@@ -880,19 +960,80 @@ int launch_cfg(const TcLaunch& L, cudaStream_t st) {
     int64_t g = (int64_t)sm_count() * C::kCtasPerSm;
     if (L.max_units < g) g = L.max_units;
     if (g < 1) g = 1;
+    const bool clustered = L.p.cluster_size > 1;
+    if (clustered) {
+        W8A16_REQUIRE(C::kClusterOk, FP8W8A16_ERR_UNSUPPORTED, "gemm_tc: cluster split-K does not fit this configuration");
+        g = L.cluster_tiles * L.p.cluster_size;
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)g);
     cfg.blockDim = dim3(kThreadsTc);
     cfg.dynamicSmemBytes = C::kSmemBytes;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;  // overlap our set-up with the previous kernel's tail
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = clustered ? (unsigned)L.p.cluster_size : 1u;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = clustered ? 2 : 1;
     const cudaError_t le = cudaLaunchKernelEx(&cfg, k_gemm_tc<BT, BK, PAIRED>, map_w, map_x, L.p);
     if (le != cudaSuccess) return fail(FP8W8A16_ERR_CUDA, "gemm_tc launch failed: %s", cudaGetErrorString(le));
     return check_launch("gemm_tc");
+}
+
+// How many clusters of `cs` CTAs of this configuration the device can hold at once (cached per device).
+template <int BT, int BK, bool PAIRED>
+int max_active_clusters(int cs) {
+    using C = TcCfg<BT, BK, PAIRED>;
+    static int cached[64][9] = {};   // 0 = not asked yet, -1 = query failed / none fit
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64 || cs < 2 || cs > 8 || !C::kClusterOk) return 0;
+    if (cached[dev][cs] == 0) {
+        cudaFuncSetAttribute(k_gemm_tc<BT, BK, PAIRED>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        cudaFuncSetAttribute(k_gemm_tc<BT, BK, PAIRED>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)(cs * 64));
+        cfg.blockDim = dim3(kThreadsTc);
+        cfg.dynamicSmemBytes = C::kSmemBytes;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = (unsigned)cs;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<BT, BK, PAIRED>, &cfg);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            n = 0;
+        }
+        // The query answers for one CTA per SM with this kernel's shared-memory size; launches place
+        // kCtasPerSm (timing a 40-tile problem: 6-CTA clusters run in one wave, 7-CTA clusters in two).
+        n *= C::kCtasPerSm;
+        cached[dev][cs] = n > 0 ? n : -1;
+    }
+    return cached[dev][cs] > 0 ? cached[dev][cs] : 0;
+}
+
+int max_active_clusters_for(int bt, bool paired, int cs) {
+    if (!paired) {
+        switch (bt) {
+            case 16: return max_active_clusters<16, 128, false>(cs);
+            case 32: return max_active_clusters<32, 128, false>(cs);
+            case 64: return max_active_clusters<64, 128, false>(cs);
+            default: return 0;
+        }
+    }
+    switch (bt) {
+        case 16: return max_active_clusters<16, 64, true>(cs);
+        case 32: return max_active_clusters<32, 64, true>(cs);
+        case 64: return max_active_clusters<64, 64, true>(cs);
+        default: return 0;
+    }
 }
 
 }  // namespace
@@ -909,6 +1050,34 @@ size_t tc_workspace_bytes(int bt, bool paired) {
 }
 
 size_t tc_max_tiles_with_tickets() { return kTicketBytes / sizeof(unsigned int); }
+
+// Cluster split-K is used when the output tiles alone cannot fill the machine: `tiles` tiles, each shared by
+// the returned number of CTAs (2..8, 0 = do not use it).  Every CTA of a cluster gets at least one K block.
+// Only sizes whose clusters are ALL resident at once are considered (the occupancy query accounts for how
+// clusters pack into the GPCs): a second wave of clusters costs far more than the fix-up it replaces.
+int tc_cluster_size(int64_t tiles, int total_kb, int bt, bool paired) {
+    // FP8W8A16_CLUSTER_SPLITK: 0 = off, n >= 2 = largest cluster a tile's K range may be split over (default 8)
+    static int max_s = -1;
+    if (max_s < 0) {
+        const char* e = getenv("FP8W8A16_CLUSTER_SPLITK");
+        max_s = e ? atoi(e) : 8;
+        if (max_s > 8) max_s = 8;
+        if (max_s < 2) max_s = 0;
+    }
+    if (!max_s || tiles <= 0 || bt > 64) return 0;
+    const int64_t capacity = tc_grid(bt, paired);
+    int64_t s = capacity / tiles;
+    if (s > max_s) s = max_s;
+    if (s > total_kb) s = total_kb;
+    for (; s >= 2; --s) {
+        if (max_active_clusters_for(bt, paired, (int)s) < tiles) continue;
+        const int per = (total_kb + (int)s - 1) / (int)s;
+        const int eff = (total_kb + per - 1) / per;   // every rank must own at least one K block
+        if (eff == (int)s) return eff;
+        if (eff >= 2 && max_active_clusters_for(bt, paired, eff) >= tiles) return eff;
+    }
+    return 0;
+}
 
 int tc_pick_bt(int rows) {
     if (rows <= 16) return 16;

@@ -32,6 +32,8 @@ struct TcParams {
     // persistent stream-K work split
     int n_token_tiles;           // dense: ceil(M / BT); grouped: read from tile_offsets[E] on the device
     int no_split;                // 1: every CTA takes whole tiles only (no partial tiles, no tickets)
+    int cluster_size;            // > 1: synchronous split-K — the CTAs of a thread-block cluster share one output tile,
+                                 //      each takes a K range, and they reduce through distributed shared memory
     float* partial;              // fp32 scratch: [gridDim.x][2][(1|2)][BT][128]
     unsigned int* tickets;       // one counter per output tile, zero on entry and on exit
 };
@@ -42,6 +44,7 @@ struct TcLaunch {
     const __half* x;
     int64_t w_total_rows;        // num_experts * w_rows_per_expert
     int64_t max_units;           // upper bound on (output tiles x K blocks): caps the grid
+    int64_t cluster_tiles;       // cluster split-K: number of clusters (= output tiles, or their upper bound)
 };
 
 int tc_pick_bt(int rows);
@@ -51,6 +54,7 @@ int tc_ctas_per_sm(int bt, bool paired);
 int tc_grid(int bt, bool paired);
 size_t tc_workspace_bytes(int bt, bool paired);
 size_t tc_max_tiles_with_tickets();
+int tc_cluster_size(int64_t tiles, int total_kb, int bt, bool paired);
 int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st);
 int tc_read_status(int* out, int reset);
 
