@@ -41,6 +41,50 @@ def _worker(rank, world, port, q):
         y_ref = olin.oracle_linear_fp32(h_full, w2, s2, bh)
         st = olin.error_stats(y.cpu(), y_ref)
         res["tp_row_allreduce"] = st["rel_rms"] < 1.5e-2 and st["finite"]
+        # ---- row-parallel GEMM with the all-reduce fused into the kernel (peer memory) ----
+        comm = par.make_peer_comm(max_out_elems=256 * 5120, max_tiles=2048)
+        fused_ok, same_ok = True, True
+        cases = [(9, 1024, 512), (1, 5120, 5120), (8, 5120, 5120), (64, 5120, 25600), (200, 1024, 2048), (8, 1000, 1024)]
+        for ci, (Mf, Nf, Kf) in enumerate(cases):
+            xf, wf, sf, bhf = make_dense(Mf, Nf, Kf, seed=20 + ci)
+            wsh, ssh = par.shard_row_parallel(wf, sf, world, rank)
+            k_per = Kf // world
+            xs = xf[:, rank * k_per:(rank + 1) * k_per].contiguous().cuda()
+            lay = par.TensorParallelLinear(wsh.cuda(), ssh.cuda(), bhf, "row", comm=comm)
+            ref = olin.oracle_linear_fp32(xf, wf, sf, bhf)
+            for rep in range(3):                      # both buffer parities, repeated launches
+                yf = lay.forward(xs)
+            stf = olin.error_stats(yf.cpu(), ref)
+            fused_ok = fused_ok and stf["rel_rms"] < 1.5e-2 and stf["finite"]
+            both = [torch.empty_like(yf) for _ in range(world)]
+            dist.all_gather(both, yf)
+            same_ok = same_ok and all(torch.equal(both[0], b) for b in both[1:])
+        res["fused_allreduce"] = fused_ok
+        res["fused_allreduce_identical_on_all_ranks"] = same_ok
+        # CUDA-graph replay of a fused call (the launch counter lives on the device)
+        xf, wf, sf, bhf = make_dense(4, 5120, 5120, seed=31)
+        wsh, ssh = par.shard_row_parallel(wf, sf, world, rank)
+        xs = xf[:, rank * (5120 // world):(rank + 1) * (5120 // world)].contiguous().cuda()
+        lay = par.TensorParallelLinear(wsh.cuda(), ssh.cuda(), bhf, "row", comm=comm)
+        yg = torch.empty((4, 5120), dtype=torch.float16, device="cuda")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ops.w8a16_linear_allreduce(comm, xs, lay.w, lay.s, lay.N, lay.K, bhf, 128, out=yg)   # warm-up on the capture stream
+            side.synchronize()
+            dist.barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                ops.w8a16_linear_allreduce(comm, xs, lay.w, lay.s, lay.N, lay.K, bhf, 128, out=yg)
+                ops.w8a16_linear_allreduce(comm, xs, lay.w, lay.s, lay.N, lay.K, bhf, 128, out=yg)
+            for _ in range(3):
+                g.replay()
+            side.synchronize()
+        torch.cuda.current_stream().wait_stream(side)
+        stg = olin.error_stats(yg.cpu(), olin.oracle_linear_fp32(xf, wf, sf, bhf))
+        res["fused_allreduce_graph"] = stg["rel_rms"] < 1.5e-2 and stg["finite"]
+        dist.barrier()
+        comm.close()
         # ---- MoE EP: each rank brings its own tokens ----
         E, I, H, topk, M = 16, 128, 256, 4, 12
         base = make_moe(E, I, H, 1, topk, seed=99)

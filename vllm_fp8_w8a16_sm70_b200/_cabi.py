@@ -18,6 +18,7 @@ SCALE_F16, SCALE_F32 = 0, 1
 DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 ALGO_AUTO, ALGO_GEMV, ALGO_TC = 0, 1, 2
 ACT_SILU, ACT_GELU = 1, 2
+COMM_HANDLE_BYTES = 64
 
 # name -> (restype, argtypes); mirrors include/fp8w8a16_b200.h one to one
 PROTOTYPES = {
@@ -32,6 +33,15 @@ PROTOTYPES = {
     "fp8w8a16_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_void_p, c_size_t, c_void_p]),
     "fp8w8a16_linear_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "fp8w8a16_comm_create": (c_int, [c_int, c_int, c_int64, c_int, ctypes.c_uint, POINTER(c_void_p)]),
+    "fp8w8a16_comm_export": (c_int, [c_void_p, c_void_p]),
+    "fp8w8a16_comm_attach": (c_int, [c_void_p, c_int, c_void_p]),
+    "fp8w8a16_comm_attach_ptr": (c_int, [c_void_p, c_int, c_void_p]),
+    "fp8w8a16_comm_base": (c_void_p, [c_void_p]),
+    "fp8w8a16_comm_bytes": (c_size_t, [c_void_p]),
+    "fp8w8a16_comm_destroy": (c_int, [c_void_p]),
+    "fp8w8a16_linear_allreduce": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                                          c_int, c_void_p, c_size_t, c_void_p]),
     "fp8w8a16_moe_topk_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "fp8w8a16_moe_align": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p]),

@@ -62,7 +62,7 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
             sys.stderr.write(out)
     if failed:
         raise RuntimeError("nvcc compilation failed")
-    cmd = [_nvcc(), "-shared", "-o", str(LIB_PATH), *map(str, objs), "-cudart", "static"]
+    cmd = [_nvcc(), "-shared", "-Wno-deprecated-gpu-targets", "-o", str(LIB_PATH), *map(str, objs), "-cudart", "static"]
     subprocess.run(cmd, check=True)
     return LIB_PATH
 

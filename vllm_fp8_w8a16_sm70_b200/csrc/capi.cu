@@ -5,6 +5,7 @@
 #include <string.h>
 
 #include <atomic>
+#include <new>
 
 #include "common.cuh"
 #include "gemm_tc.h"
@@ -112,7 +113,7 @@ int check_common(const void* x, const void* w, const void* scales, const void* o
 }
 
 int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_dtype, __half* out, int M, int N, int K,
-              int block_h, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+              int block_h, void* workspace, size_t workspace_bytes, cudaStream_t st, const ArParams* ar = nullptr) {
     const int bt = dense_token_tile(M), bk = tc_block_k(bt, false);
     const int token_tiles = (M + bt - 1) / bt;
     const int64_t tiles = (int64_t)((N + 127) / 128) * token_tiles;
@@ -146,6 +147,16 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
     W8A16_REQUIRE(L.max_units < (1ll << 31), FP8W8A16_ERR_UNSUPPORTED, "linear: problem too large for 32-bit work indices");
     L.p.cluster_size = tc_cluster_size(tiles, (K + bk - 1) / bk, bt, false);
     L.cluster_tiles = tiles;
+    if (ar != nullptr && ar->world > 1) {
+        W8A16_REQUIRE(N % 4 == 0, FP8W8A16_ERR_UNSUPPORTED, "linear_allreduce: N must be a multiple of 4 (got %d)", N);
+        W8A16_REQUIRE(tiles * kArChunks <= ar->slots, FP8W8A16_ERR_UNSUPPORTED,
+                      "linear_allreduce: %lld output tiles exceed the communicator's %d flag slots", (long long)tiles, ar->slots);
+        W8A16_REQUIRE((int64_t)M * N <= ar->part_elems, FP8W8A16_ERR_UNSUPPORTED,
+                      "linear_allreduce: M*N = %lld exceeds the communicator's buffer of %lld elements", (long long)M * N,
+                      (long long)ar->part_elems);
+        L.ar = *ar;
+        L.ar.out = out;
+    }
     return tc_launch(L, bt, false, st);
 }
 
@@ -235,6 +246,34 @@ MoeLayout moe_layout(int M, int topk, int E, int H, int I) {
     L.y_sorted = take((size_t)R * H * 2);
     L.total = o;
     return L;
+}
+
+
+// ---- peer-memory communicator of the fused row-parallel GEMM + all-reduce ---------------------------------
+// One cudaMalloc per rank with the same layout on every rank: control words, flag array, two partial buffers.
+struct Comm {
+    int rank, world, slots, device;
+    unsigned int timeout_ms;
+    int64_t part_elems;
+    size_t flags_off, part_off, bytes;
+    char* base[kArMaxWorld];     // base[rank] is the local allocation, the others are the peers' mappings
+    bool ipc_opened[kArMaxWorld];
+};
+
+int comm_params(const Comm* c, ArParams* ar) {
+    memset(ar, 0, sizeof(*ar));
+    ar->world = c->world;
+    ar->rank = c->rank;
+    ar->timeout_ms = c->timeout_ms;
+    ar->slots = c->slots;
+    ar->part_elems = c->part_elems;
+    ar->ctrl = reinterpret_cast<unsigned int*>(c->base[c->rank]);
+    for (int r = 0; r < c->world; ++r) {
+        W8A16_REQUIRE(c->base[r] != nullptr, FP8W8A16_ERR_INVALID, "comm: rank %d is not attached", r);
+        ar->flags[r] = reinterpret_cast<unsigned int*>(c->base[r] + c->flags_off);
+        ar->part[r] = reinterpret_cast<__half*>(c->base[r] + c->part_off);
+    }
+    return 0;
 }
 
 }  // namespace
@@ -424,6 +463,106 @@ int fp8w8a16_moe_forward(const uint16_t* x, const void* topk_ids, int ids_are_i6
                       ws + L.gemm_ws, L.gemm_ws_bytes, st);
     if (rc) return rc;
     return launch_combine(y_sorted, inv_pos, M, topk, H, reinterpret_cast<__half*>(out), st);
+}
+
+// ---- fused row-parallel linear + all-reduce over peer memory ---------------------------------------------
+struct fp8w8a16_comm {
+    w8a16::Comm c;
+};
+
+int fp8w8a16_comm_create(int rank, int world, int64_t max_out_elems, int max_tiles, unsigned int timeout_ms,
+                         fp8w8a16_comm** comm) {
+    W8A16_REQUIRE(comm != nullptr, FP8W8A16_ERR_INVALID, "comm_create: null output pointer");
+    *comm = nullptr;
+    W8A16_REQUIRE(world >= 2 && world <= kArMaxWorld && rank >= 0 && rank < world, FP8W8A16_ERR_INVALID,
+                  "comm_create: rank %d of world %d (2..%d ranks supported)", rank, world, kArMaxWorld);
+    W8A16_REQUIRE(max_out_elems > 0 && max_tiles > 0 && max_tiles <= (1 << 20), FP8W8A16_ERR_INVALID,
+                  "comm_create: max_out_elems=%lld max_tiles=%d", (long long)max_out_elems, max_tiles);
+    fp8w8a16_comm* h = new (std::nothrow) fp8w8a16_comm();
+    W8A16_REQUIRE(h != nullptr, FP8W8A16_ERR_CUDA, "comm_create: out of host memory");
+    Comm& c = h->c;
+    memset(&c, 0, sizeof(c));
+    c.rank = rank;
+    c.world = world;
+    c.slots = max_tiles * kArChunks;
+    c.timeout_ms = timeout_ms ? timeout_ms : 2000u;
+    c.part_elems = (max_out_elems + 127) / 128 * 128;
+    c.flags_off = 256;
+    c.part_off = align_up(c.flags_off + (size_t)world * c.slots * sizeof(unsigned int), 256);
+    c.bytes = c.part_off + 2 * (size_t)c.part_elems * sizeof(__half);
+    cudaError_t e = cudaGetDevice(&c.device);
+    void* base = nullptr;
+    if (e == cudaSuccess) e = cudaMalloc(&base, c.bytes);
+    if (e == cudaSuccess) e = cudaMemset(base, 0, c.bytes);
+    if (e != cudaSuccess) {
+        if (base) cudaFree(base);
+        delete h;
+        return fail(FP8W8A16_ERR_CUDA, "comm_create: %s", cudaGetErrorString(e));
+    }
+    c.base[rank] = reinterpret_cast<char*>(base);
+    *comm = h;
+    return 0;
+}
+
+int fp8w8a16_comm_export(const fp8w8a16_comm* comm, void* handle) {
+    W8A16_REQUIRE(comm && handle, FP8W8A16_ERR_INVALID, "comm_export: null pointer");
+    static_assert(sizeof(cudaIpcMemHandle_t) == FP8W8A16_COMM_HANDLE_BYTES, "handle size");
+    cudaIpcMemHandle_t hd;
+    W8A16_CUDA(cudaIpcGetMemHandle(&hd, comm->c.base[comm->c.rank]));
+    memcpy(handle, &hd, sizeof(hd));
+    return 0;
+}
+
+int fp8w8a16_comm_attach(fp8w8a16_comm* comm, int peer, const void* handle) {
+    W8A16_REQUIRE(comm && handle, FP8W8A16_ERR_INVALID, "comm_attach: null pointer");
+    Comm& c = comm->c;
+    W8A16_REQUIRE(peer >= 0 && peer < c.world && peer != c.rank, FP8W8A16_ERR_INVALID, "comm_attach: bad peer %d", peer);
+    W8A16_REQUIRE(c.base[peer] == nullptr, FP8W8A16_ERR_INVALID, "comm_attach: peer %d is already attached", peer);
+    cudaIpcMemHandle_t hd;
+    memcpy(&hd, handle, sizeof(hd));
+    void* ptr = nullptr;
+    W8A16_CUDA(cudaIpcOpenMemHandle(&ptr, hd, cudaIpcMemLazyEnablePeerAccess));
+    c.base[peer] = reinterpret_cast<char*>(ptr);
+    c.ipc_opened[peer] = true;
+    return 0;
+}
+
+int fp8w8a16_comm_attach_ptr(fp8w8a16_comm* comm, int peer, void* peer_base) {
+    W8A16_REQUIRE(comm && peer_base, FP8W8A16_ERR_INVALID, "comm_attach_ptr: null pointer");
+    Comm& c = comm->c;
+    W8A16_REQUIRE(peer >= 0 && peer < c.world && peer != c.rank, FP8W8A16_ERR_INVALID, "comm_attach_ptr: bad peer %d", peer);
+    W8A16_REQUIRE(c.base[peer] == nullptr, FP8W8A16_ERR_INVALID, "comm_attach_ptr: peer %d is already attached", peer);
+    c.base[peer] = reinterpret_cast<char*>(peer_base);
+    c.ipc_opened[peer] = false;
+    return 0;
+}
+
+void* fp8w8a16_comm_base(const fp8w8a16_comm* comm) { return comm ? comm->c.base[comm->c.rank] : nullptr; }
+
+size_t fp8w8a16_comm_bytes(const fp8w8a16_comm* comm) { return comm ? comm->c.bytes : 0; }
+
+int fp8w8a16_comm_destroy(fp8w8a16_comm* comm) {
+    if (comm == nullptr) return 0;
+    Comm& c = comm->c;
+    for (int r = 0; r < c.world; ++r)
+        if (r != c.rank && c.base[r] != nullptr && c.ipc_opened[r]) cudaIpcCloseMemHandle(c.base[r]);
+    if (c.base[c.rank] != nullptr) cudaFree(c.base[c.rank]);
+    delete comm;
+    return 0;
+}
+
+int fp8w8a16_linear_allreduce(fp8w8a16_comm* comm, const uint16_t* x, const uint8_t* w, const void* scales, int scale_dtype,
+                              uint16_t* out, int M, int N, int K, int block_h, int block_w, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+    W8A16_REQUIRE(comm != nullptr, FP8W8A16_ERR_INVALID, "linear_allreduce: null communicator");
+    int rc = check_common(x, w, scales, out, M, N, K, block_h, block_w, scale_dtype);
+    if (rc) return rc;
+    if (M == 0 || N == 0) return 0;
+    ArParams ar;
+    rc = comm_params(&comm->c, &ar);
+    if (rc) return rc;
+    return linear_tc(reinterpret_cast<const __half*>(x), w, scales, scale_dtype, reinterpret_cast<__half*>(out), M, N, K,
+                     block_h, workspace, workspace_bytes, (cudaStream_t)stream, &ar);
 }
 
 }  // extern "C"

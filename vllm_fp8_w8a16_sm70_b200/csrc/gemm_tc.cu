@@ -240,6 +240,40 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
     return v;
 }
 
+// System-scope flag traffic and peer-memory loads of the fused all-reduce.
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ uint2 ld_relaxed_sys_u2(const void* p) {
+    uint2 v;
+    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+// Bounded wait until the flag has reached `epoch` (epochs only grow; a peer may already be one launch ahead).
+__device__ __forceinline__ bool ar_wait_flag(const unsigned int* flag, unsigned int epoch, unsigned int timeout_ms,
+                                             volatile int* dead) {
+    const unsigned long long t0 = globaltimer_ns();
+    const unsigned long long limit = (unsigned long long)timeout_ms * 1000000ull;
+    uint32_t spins = 0;
+    while ((int)(ld_acquire_sys(flag) - epoch) < 0) {
+        if ((++spins & 0xFu) == 0u) {
+            if (*dead) return false;
+            if (globaltimer_ns() - t0 > limit) {
+                *dead = 1;
+                atomicOr(&g_tc_status, 128);
+                return false;
+            }
+            __nanosleep(64);
+        }
+    }
+    return true;
+}
+
 // ---- compile-time configuration ------------------------------------------------------------------
 // TMEM columns of one CTA: kAccBufs accumulator buffers of kAccCols fp32 columns (BT per weight
 // tile; two buffers where they fit, so the epilogue of one segment overlaps the MMAs of the next),
@@ -300,7 +334,7 @@ __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + 
 // (src/fp8_w8a16_sm70/vllm_serve.py:1953-1990): GEMM output -> FP16, SiLU on FP16, product FP16,
 // route weight as FP16.
 template <bool PAIRED>
-__device__ __forceinline__ void store_out(const TcParams& p, int row, int n, float g, float u) {
+__device__ __forceinline__ void store_out(const TcParams& p, __half* out, int row, int n, float g, float u) {
     __half r;
     if (PAIRED) {
         const __half g16 = __float2half_rn(g), u16 = __float2half_rn(u);
@@ -314,7 +348,7 @@ __device__ __forceinline__ void store_out(const TcParams& p, int row, int n, flo
             r = __float2half_rn(__half2float(r) * __half2float(w16));
         }
     }
-    p.out[(int64_t)row * p.ldo + n] = r;
+    out[(int64_t)row * p.ldo + n] = r;
 }
 
 // ---- work decomposition ------------------------------------------------------------------------------
@@ -374,9 +408,11 @@ __device__ __forceinline__ int partial_slot(int c, int tile, int total_kb, int u
 }
 
 // ---- the kernel --------------------------------------------------------------------------------
-template <int BT, int BK, bool PAIRED>
+template <int BT, int BK, bool PAIRED, bool AR>
 __global__ void __launch_bounds__(kThreadsTc, TcCfg<BT, BK, PAIRED>::kCtasPerSm)
-k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p) {
+k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, const TcParams p,
+          const ArParams ar) {
+    static_assert(!(AR && PAIRED), "the fused all-reduce is a dense (row-parallel) mode");
     using C = TcCfg<BT, BK, PAIRED>;
     constexpr int kNS = C::kNS, kNA = C::kNA;
 
@@ -495,6 +531,14 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         set_range();
     }
     const bool has_work = u_begin < u_end;  // uniform for the whole CTA
+    // Fused all-reduce: this launch's epoch (one more than the count of finished fused launches; every rank
+    // makes the same sequence of launches) selects the partial buffer the GEMM result is left in.
+    unsigned int ar_epoch = 0;
+    __half* out_ptr = p.out;
+    if (AR) {
+        ar_epoch = *reinterpret_cast<volatile unsigned int*>(ar.ctrl) + 1u;
+        out_ptr = ar.part[ar.rank] + (int64_t)(ar_epoch & 1u) * ar.part_elems;
+    }
 
     if (!has_work) {
         // nothing to do: fall through to the teardown (TMEM must still be returned)
@@ -599,6 +643,57 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         (void)tr_i;
         bool ok = true;
 
+        // Fused all-reduce of one finished region of an output tile (16-byte groups [lo, hi) of the BT x 128 tile;
+        // `chunk` tells the regions of a tile apart).  Called by all 256 threads.  This rank's FP16 partial values
+        // are already stored in its partial buffer: publish them (barrier, system-scope fence, one flag per peer),
+        // wait - bounded - for every peer's flag of the same region, then add the peers' values over NVLink in
+        // ascending rank order and store the sum.  A peer's buffer of this parity is not rewritten before this
+        // rank has raised its flags of the NEXT launch, which it does only after finishing this one.
+        auto ar_finish = [&](const Seg& sg, int chunk, int lo, int hi, int dead_in) -> int {
+            if (!AR) return dead_in;
+            const int slot = sg.tile * kArChunks + chunk;
+            epi_bar_sync();
+            if (td == 0 && !dead_in) {
+                __threadfence_system();
+                for (int r = 0; r < ar.world; ++r)
+                    if (r != ar.rank) st_release_sys(ar.flags[r] + (int64_t)ar.rank * ar.slots + slot, ar_epoch);
+            }
+            if (td < ar.world && td != ar.rank && !dead_in)
+                ar_wait_flag(ar.flags[ar.rank] + (int64_t)td * ar.slots + slot, ar_epoch, ar.timeout_ms, s_dead);
+            epi_bar_sync();
+            const int dead = dead_in | *s_dead;
+            if (dead) return dead;
+            const int n0 = sg.slab * 128;
+            const int64_t par = (int64_t)(ar_epoch & 1u) * ar.part_elems;
+            for (int idx4 = lo + td; idx4 < hi; idx4 += kDequantThreads) {
+                const int ml = idx4 >> 5, nl = (idx4 & 31) * 4;
+                if (ml >= sg.rows_valid || n0 + nl >= p.N) continue;
+                const int64_t off = (int64_t)(sg.row_begin + ml) * p.ldo + n0 + nl;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+                for (int r0 = 0; r0 < ar.world; r0 += 4) {         // four peers' loads in flight, added in rank order
+                    uint2 v[4];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+                        if (r0 + r < ar.world) v[r] = ld_relaxed_sys_u2(ar.part[r0 + r] + par + off);
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) {
+                        if (r0 + r < ar.world) {
+                            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v[r].x));
+                            const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v[r].y));
+                            acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+                        }
+                    }
+                }
+                const __half2 o0 = __floats2half2_rn(acc.x, acc.y), o1 = __floats2half2_rn(acc.z, acc.w);
+                uint2 o;
+                o.x = *reinterpret_cast<const uint32_t*>(&o0);
+                o.y = *reinterpret_cast<const uint32_t*>(&o1);
+                *reinterpret_cast<uint2*>(ar.out + off) = o;
+            }
+            return dead;
+        };
+
         // Epilogue of one finished segment: TMEM -> registers -> FP16 output, or fp32 partial tile + ticket
         // + (for the last contributor) the fixed-order reduction.  Returns the CTA-wide "dead" flag that
         // thread 0 publishes; every one of the 256 threads calls it once per segment and takes both
@@ -636,7 +731,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             if (col + j < sg.rows_valid && n < p.N)
-                                store_out<PAIRED>(p, sg.row_begin + col + j, n, g[j], PAIRED ? uu[j] : 0.f);
+                                store_out<PAIRED>(p, out_ptr, sg.row_begin + col + j, n, g[j], PAIRED ? uu[j] : 0.f);
                     } else if (clustered) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -702,13 +797,15 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         }
                     }
                     const int row = sg.row_begin + ml, n = n0 + nl;
-                    store_out<PAIRED>(p, row, n, g.x, uu.x);
-                    if (n + 1 < p.N) store_out<PAIRED>(p, row, n + 1, g.y, uu.y);
-                    if (n + 2 < p.N) store_out<PAIRED>(p, row, n + 2, g.z, uu.z);
-                    if (n + 3 < p.N) store_out<PAIRED>(p, row, n + 3, g.w, uu.w);
+                    store_out<PAIRED>(p, out_ptr, row, n, g.x, uu.x);
+                    if (n + 1 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 1, g.y, uu.y);
+                    if (n + 2 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 2, g.z, uu.z);
+                    if (n + 3 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 3, g.w, uu.w);
                 }
                 if (td == 0) p.tickets[sg.tile] = 0u;  // leave the counter clean for the next launch
+                if (AR) return ar_finish(sg, 0, 0, BT * 32, dead_now);
             }
+            if (AR && direct) return ar_finish(sg, 0, 0, BT * 32, dead_now);
             return dead_now;
         };
 
@@ -835,13 +932,22 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         }
                     }
                     const int row = last_sg.row_begin + ml, n = n0 + nl;
-                    store_out<PAIRED>(p, row, n, g.x, uu.x);
-                    if (n + 1 < p.N) store_out<PAIRED>(p, row, n + 1, g.y, uu.y);
-                    if (n + 2 < p.N) store_out<PAIRED>(p, row, n + 2, g.z, uu.z);
-                    if (n + 3 < p.N) store_out<PAIRED>(p, row, n + 3, g.w, uu.w);
+                    store_out<PAIRED>(p, out_ptr, row, n, g.x, uu.x);
+                    if (n + 1 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 1, g.y, uu.y);
+                    if (n + 2 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 2, g.z, uu.z);
+                    if (n + 3 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 3, g.w, uu.w);
                 }
             }
             cluster_sync_all();   // nobody leaves (and frees its shared memory) while a peer may still read it
+            if (AR) {
+                Seg last_sg;
+                get_seg<BT>(p, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
+                uint32_t rnk;
+                asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rnk));
+                const int chunk = (BT * 32 + p.cluster_size - 1) / p.cluster_size;
+                const int lo = (int)rnk * chunk, hi = min(BT * 32, lo + chunk);
+                if (lo < hi) stop = ar_finish(last_sg, (int)rnk, lo, hi, stop);
+            }
         }
     }
 
@@ -863,6 +969,16 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
+    }
+    if (AR && threadIdx.x == 0) {
+        // the last CTA of the grid to get here closes the launch: the epoch every CTA read above is now finished
+        __threadfence();
+        const unsigned int prev = atomicAdd(&ar.ctrl[1], 1u);
+        if (prev == gridDim.x - 1) {
+            ar.ctrl[1] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile unsigned int*>(ar.ctrl) = ar_epoch;
+        }
     }
 #ifdef W8A16_TC_TRACE
     if (threadIdx.x == 0 && blockIdx.x < 512) g_tc_cta[blockIdx.x][3] = globaltimer_ns_raw();
@@ -940,15 +1056,15 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const vo
     return 0;
 }
 
-template <int BT, int BK, bool PAIRED>
+template <int BT, int BK, bool PAIRED, bool AR>
 int launch_cfg(const TcLaunch& L, cudaStream_t st) {
     using C = TcCfg<BT, BK, PAIRED>;
     static bool attr_set[64] = {};
     int dev = 0;
     W8A16_CUDA(cudaGetDevice(&dev));
     if (dev < 64 && !attr_set[dev]) {
-        W8A16_CUDA(cudaFuncSetAttribute(k_gemm_tc<BT, BK, PAIRED>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
-        W8A16_CUDA(cudaFuncSetAttribute(k_gemm_tc<BT, BK, PAIRED>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+        W8A16_CUDA(cudaFuncSetAttribute(k_gemm_tc<BT, BK, PAIRED, AR>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes));
+        W8A16_CUDA(cudaFuncSetAttribute(k_gemm_tc<BT, BK, PAIRED, AR>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
         attr_set[dev] = true;
     }
     CUtensorMap map_w, map_x;
@@ -979,7 +1095,7 @@ int launch_cfg(const TcLaunch& L, cudaStream_t st) {
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = clustered ? 2 : 1;
-    const cudaError_t le = cudaLaunchKernelEx(&cfg, k_gemm_tc<BT, BK, PAIRED>, map_w, map_x, L.p);
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, k_gemm_tc<BT, BK, PAIRED, AR>, map_w, map_x, L.p, L.ar);
     if (le != cudaSuccess) return fail(FP8W8A16_ERR_CUDA, "gemm_tc launch failed: %s", cudaGetErrorString(le));
     return check_launch("gemm_tc");
 }
@@ -992,8 +1108,8 @@ int max_active_clusters(int cs) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev >= 64 || cs < 2 || cs > 8 || !C::kClusterOk) return 0;
     if (cached[dev][cs] == 0) {
-        cudaFuncSetAttribute(k_gemm_tc<BT, BK, PAIRED>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
-        cudaFuncSetAttribute(k_gemm_tc<BT, BK, PAIRED>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        cudaFuncSetAttribute(k_gemm_tc<BT, BK, PAIRED, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        cudaFuncSetAttribute(k_gemm_tc<BT, BK, PAIRED, false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3((unsigned)(cs * 64));
         cfg.blockDim = dim3(kThreadsTc);
@@ -1006,7 +1122,7 @@ int max_active_clusters(int cs) {
         cfg.attrs = attr;
         cfg.numAttrs = 1;
         int n = 0;
-        const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<BT, BK, PAIRED>, &cfg);
+        const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, k_gemm_tc<BT, BK, PAIRED, false>, &cfg);
         if (e != cudaSuccess) {
             (void)cudaGetLastError();
             n = 0;
@@ -1088,8 +1204,18 @@ int tc_pick_bt(int rows) {
 }
 
 int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st) {
-#define W8A16_TC_CASE(BT_, BK_, P_) return launch_cfg<BT_, BK_, P_>(L, st)
-    if (!paired) {
+#define W8A16_TC_CASE(BT_, BK_, P_) return launch_cfg<BT_, BK_, P_, false>(L, st)
+#define W8A16_TC_CASE_AR(BT_, BK_) return launch_cfg<BT_, BK_, false, true>(L, st)
+    if (L.ar.world > 1) {
+        W8A16_REQUIRE(!paired, FP8W8A16_ERR_UNSUPPORTED, "gemm_tc: the fused all-reduce is a dense mode");
+        switch (bt) {
+            case 16: W8A16_TC_CASE_AR(16, 128);
+            case 32: W8A16_TC_CASE_AR(32, 128);
+            case 64: W8A16_TC_CASE_AR(64, 128);
+            case 128: W8A16_TC_CASE_AR(128, 64);
+            case 256: W8A16_TC_CASE_AR(256, 64);
+        }
+    } else if (!paired) {
         switch (bt) {
             case 16: W8A16_TC_CASE(16, 128, false);
             case 32: W8A16_TC_CASE(32, 128, false);
@@ -1105,6 +1231,7 @@ int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st) {
             case 128: W8A16_TC_CASE(128, 64, true);
         }
     }
+#undef W8A16_TC_CASE_AR
 #undef W8A16_TC_CASE
     return fail(FP8W8A16_ERR_UNSUPPORTED, "gemm_tc: unsupported token tile %d", bt);
 }

@@ -38,8 +38,27 @@ struct TcParams {
     unsigned int* tickets;       // one counter per output tile, zero on entry and on exit
 };
 
+// Fused all-reduce of a row-parallel GEMM over peer memory (one process per GPU, buffers mapped through CUDA IPC).
+// Every rank runs the same launch.  A finished output tile is left as FP16 in the rank's own partial buffer, a flag is
+// stored into every peer's flag array, and the CTA that finished the tile waits for the peers' flags of the SAME tile,
+// loads their partial tiles over NVLink and adds them in ascending rank order (identical result on every rank).
+constexpr int kArMaxWorld = 8;
+constexpr int kArChunks = 8;          // flag slots per output tile (one per CTA of a split-K cluster)
+struct ArParams {
+    int world;                        // 0 = not fused
+    int rank;
+    unsigned int timeout_ms;          // bound of the wait for a peer's flag
+    int slots;                        // flag slots per source rank
+    unsigned int* ctrl;               // local: [0] = number of finished fused launches (epoch), [1] = CTAs done in this launch
+    unsigned int* flags[kArMaxWorld]; // flags[r]: rank r's flag array [world][slots] (entry [s][i]: epoch of source s, slot i)
+    __half* part[kArMaxWorld];        // part[r]: rank r's partial buffers [2][part_elems] (parity = epoch & 1)
+    int64_t part_elems;
+    __half* out;                      // reduced output [M, N] (local)
+};
+
 struct TcLaunch {
     TcParams p;
+    ArParams ar;
     const uint8_t* w;
     const __half* x;
     int64_t w_total_rows;        // num_experts * w_rows_per_expert

@@ -195,6 +195,86 @@ def w8a16_linear_noalloc(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor,
 
 
 # ------------------------------------------------------------------------------------------------
+# row-parallel linear with the all-reduce fused into the GEMM kernel (peer memory over NVLink)
+# ------------------------------------------------------------------------------------------------
+class PeerComm:
+    """One rank's end of the peer-memory communicator (``fp8w8a16_comm_*``): a device buffer (flags + two FP16
+    partial buffers) that the other ranks' GPUs map through CUDA IPC.  ``handle()`` is the 64-byte IPC handle to send
+    to the peers by any host channel; ``attach(peer, handle)`` maps a peer's buffer.  All ranks must then make the
+    same sequence of ``w8a16_linear_allreduce`` calls."""
+
+    def __init__(self, rank: int, world: int, max_out_elems: int, max_tiles: int = 4096, timeout_ms: int = 2000,
+                 device: Optional[torch.device] = None):
+        import ctypes
+        self.rank, self.world = rank, world
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if self.device.type != "cuda":
+            raise RuntimeError("PeerComm needs a CUDA device (there is no CPU path)")
+        self._h = ctypes.c_void_p()
+        with _dev_guard(self.device):
+            _cabi.check(_cabi.load().fp8w8a16_comm_create(rank, world, max_out_elems, max_tiles, timeout_ms,
+                                                         ctypes.byref(self._h)), "fp8w8a16_comm_create")
+
+    def handle(self) -> bytes:
+        import ctypes
+        buf = ctypes.create_string_buffer(_cabi.COMM_HANDLE_BYTES)
+        with _dev_guard(self.device):
+            _cabi.check(_cabi.load().fp8w8a16_comm_export(self._h, buf), "fp8w8a16_comm_export")
+        return buf.raw
+
+    def attach(self, peer: int, handle: bytes) -> None:
+        import ctypes
+        buf = ctypes.create_string_buffer(handle, _cabi.COMM_HANDLE_BYTES)
+        with _dev_guard(self.device):
+            _cabi.check(_cabi.load().fp8w8a16_comm_attach(self._h, peer, buf), "fp8w8a16_comm_attach")
+
+    def attach_ptr(self, peer: int, base: int) -> None:
+        _cabi.check(_cabi.load().fp8w8a16_comm_attach_ptr(self._h, peer, base), "fp8w8a16_comm_attach_ptr")
+
+    @property
+    def base(self) -> int:
+        return int(_cabi.load().fp8w8a16_comm_base(self._h) or 0)
+
+    @property
+    def nbytes(self) -> int:
+        return int(_cabi.load().fp8w8a16_comm_bytes(self._h))
+
+    def close(self) -> None:
+        if self._h is not None and self._h.value:
+            with _dev_guard(self.device):
+                _cabi.load().fp8w8a16_comm_destroy(self._h)
+            self._h = None
+
+
+def w8a16_linear_allreduce(comm: PeerComm, x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, N: int, K: int,
+                           block_h: int = 128, block_w: int = 128, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """This rank's K shard of a row-parallel linear, x [M, K_shard] @ dequant(w [N, K_shard])^T, summed over the ranks
+    of ``comm`` inside the GEMM kernel: one launch replaces apply + all-reduce
+    (src/fp8_w8a16_sm70/vllm_serve.py:2922-2959).  The result is bit-identical on every rank."""
+    w = _as_u8(w)
+    dev = _require_cuda(x, w, scales)
+    if x.dtype != torch.float16:
+        raise RuntimeError(f"x must be float16 (got {x.dtype})")
+    if x.dim() != 2 or x.shape[1] != K or w.numel() != N * K:
+        raise RuntimeError(f"shape mismatch: x {tuple(x.shape)}, w {w.numel()} elements, N={N} K={K}")
+    M = x.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.float16, device=dev)
+    lib = _cabi.load()
+    with _dev_guard(dev):
+        st = _stream(dev)
+        need = _LINEAR_WS_BYTES.get((M, N, K))
+        if need is None:
+            need = _LINEAR_WS_BYTES[(M, N, K)] = lib.fp8w8a16_linear_workspace_bytes(M, N, K)
+        ws = workspace(dev, need, st)
+        rc = lib.fp8w8a16_linear_allreduce(comm._h, x.data_ptr(), w.data_ptr(), scales.data_ptr(), _scale_dtype(scales),
+                                           out.data_ptr(), M, N, K, block_h, block_w, ws.data_ptr(), ws.numel(), st)
+        if rc:
+            _cabi.check(rc, "fp8w8a16_linear_allreduce")
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
 # MoE
 # ------------------------------------------------------------------------------------------------
 _LOGIT_DTYPES = {torch.float32: _cabi.DTYPE_F32, torch.float16: _cabi.DTYPE_F16, torch.bfloat16: _cabi.DTYPE_BF16}

@@ -7,8 +7,8 @@ MoE: experts, then reduce — ``:2785-2853``).  Expert parallelism is only *tole
 (``expert_map`` + a later reduce, ``:2237-2243``); the all-to-all dispatch / combine below is new,
 and its oracle is the single-GPU layer.
 
-One process per GPU.  Nothing here is a fused compute + collective kernel: the GEMMs are the
-engine's, the exchange is NCCL's.
+One process per GPU.  Row-parallel layers can run with the all-reduce fused into the GEMM kernel over peer
+memory (``make_peer_comm`` + ``TensorParallelLinear(..., comm=...)``); everything else exchanges through NCCL.
 """
 
 from __future__ import annotations
@@ -53,15 +53,19 @@ class TensorParallelLinear:
     """One rank's shard of a column- or row-parallel FP8 linear."""
 
     def __init__(self, w_shard: torch.Tensor, s_shard: torch.Tensor, block_h: int, mode: str,
-                 group: Optional[dist.ProcessGroup] = None, linear_fn: Optional[Callable] = None):
+                 group: Optional[dist.ProcessGroup] = None, linear_fn: Optional[Callable] = None,
+                 comm: Optional["ops.PeerComm"] = None):
         assert mode in ("column", "row")
         self.w, self.s, self.block_h, self.mode, self.group = w_shard, s_shard, block_h, mode, group
         self.N, self.K = int(w_shard.shape[0]), int(w_shard.shape[1])
         self._linear = linear_fn or (lambda x: ops.w8a16_linear(x, self.w, self.s, self.N, self.K, self.block_h, 128))
+        self.comm = comm if mode == "row" else None   # fused GEMM + all-reduce over peer memory
 
     def forward(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """column: x [M, K] (replicated) -> [M, N/tp].  row: x [M, K/tp] -> all-reduced [M, N]; the bias is
         added on rank 0 only before the reduce, as vLLM does."""
+        if self.comm is not None and bias is None and x.shape[0] * self.N <= self.comm_max_elems():
+            return ops.w8a16_linear_allreduce(self.comm, x, self.w, self.s, self.N, self.K, self.block_h, 128)
         y = self._linear(x)
         if self.mode == "row":
             if bias is not None and dist.get_rank(self.group) == 0:
@@ -71,6 +75,27 @@ class TensorParallelLinear:
         elif bias is not None:
             y = y + bias.to(y.dtype)
         return y
+
+
+    def comm_max_elems(self) -> int:
+        return getattr(self.comm, "max_out_elems", 0)
+
+
+def make_peer_comm(max_out_elems: int, max_tiles: int = 4096, timeout_ms: int = 2000,
+                   group: Optional[dist.ProcessGroup] = None) -> "ops.PeerComm":
+    """Collective: every rank of ``group`` creates its communicator buffer on its current CUDA device, the IPC handles
+    travel through ``all_gather_object`` and every rank maps every peer.  Ends with a barrier so that no rank launches
+    before all mappings exist."""
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    comm = ops.PeerComm(rank, world, max_out_elems, max_tiles, timeout_ms)
+    comm.max_out_elems = max_out_elems
+    handles = [None] * world
+    dist.all_gather_object(handles, comm.handle(), group=group)
+    for peer, h in enumerate(handles):
+        if peer != rank:
+            comm.attach(peer, h)
+    dist.barrier(group=group)
+    return comm
 
 
 # ------------------------------------------------------------------------------------------------
