@@ -190,10 +190,13 @@ class DenseStack:
     """Several independent copies of each of the four linears (enough bytes per shape to defeat the 126 MB
     L2 when the copies are cycled); with world > 1 every rank holds its TP shard of every copy."""
 
-    def __init__(self, world: int, rank: int, device, min_bytes: int = 320 << 20, max_copies: int = 12):
+    def __init__(self, world: int, rank: int, device, min_bytes: int = 320 << 20, max_copies: int = 12, fused: bool = True):
         from vllm_fp8_w8a16_sm70_b200 import parallel as par
         self.world, self.device = world, device
         self.copies = {}
+        # row-parallel layers: all-reduce fused into the GEMM kernel over peer memory for up to 256 tokens
+        # (larger batches, and --allreduce nccl, use NCCL after the GEMM)
+        self.comm = par.make_peer_comm(max_out_elems=256 * 5120) if (world > 1 and fused) else None
         for si, (name, N, K, mode) in enumerate(DENSE_SHAPES):
             n = max(2, min(max_copies, -(-min_bytes // (N * K // world))))
             lst = []
@@ -202,7 +205,7 @@ class DenseStack:
                 s16 = s.to(torch.float16)        # load-time cast, as process_weights_after_loading does
                 if world > 1:
                     q, s16 = (par.shard_column_parallel if mode == "column" else par.shard_row_parallel)(q, s16, world, rank)
-                lst.append(par.TensorParallelLinear(q, s16, 128, mode))
+                lst.append(par.TensorParallelLinear(q, s16, 128, mode, comm=self.comm))
                 del s
             self.copies[name] = lst
         torch.cuda.empty_cache()
@@ -221,7 +224,7 @@ def run_dense(args, world, rank, local, m_list, workload: str) -> dict:
     from vllm_fp8_w8a16_sm70_b200 import _cabi, ops
     device = torch.device("cuda", local)
     peaks = measured_peaks()
-    stack = DenseStack(world, rank, device)
+    stack = DenseStack(world, rank, device, fused=(args.allreduce == "fused"))
     xs = {M: stack.inputs(M) for M in m_list}
     lib = _cabi.load()
     use_graphs = not args.eager   # NCCL all-reduce is captured with the GEMMs when world > 1
@@ -313,7 +316,7 @@ def run_dense(args, world, rank, local, m_list, workload: str) -> dict:
         "ms_per_step": round(ms_step, 4), "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic", "impl": "ours",
         "config": {"workload": f"dense {workload} sweep: qkv[7168,5120] o[5120,5120] gate_up[51200,5120] down[5120,25600], block-128 "
-                               f"E4M3 + block scales, fp16 acts, M in {m_list}", "parallelism": f"tp{world}", "timing": timing,
+                               f"E4M3 + block scales, fp16 acts, M in {m_list}", "parallelism": f"tp{world}" + ("" if world == 1 else (" fused GEMM+all-reduce over peer memory" if stack.comm is not None else " NCCL all-reduce")), "timing": timing,
                    "l2": "inputs larger than L2: every shape cycles over >= 320 MB of distinct weight copies (126 MB L2)"},
         "roofline": roof, "e2e": e2e, "gpu_launches": int(launches), "clocks": clk.summary(), "cases": cases,
     }
@@ -337,7 +340,8 @@ def run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, wo
         for name in stack.copies:
             lin = stack.lin(name, ci)
             objs[name] = types.SimpleNamespace(weight=lin.w, weight_scale_inv=lin.s, weight_block_size=[128, 128],
-                                               input_size_per_partition=lin.K, output_size_per_partition=lin.N, mode=lin.mode)
+                                               input_size_per_partition=lin.K, output_size_per_partition=lin.N, mode=lin.mode,
+                                               w8a16_peer_comm=lin.comm, w8a16_reduced=False)
         layers.append(objs)
     # One pinned HOST buffer holds every activation matrix of a step, one holds every result: per step there is
     # one host->device copy of the inputs, the 4 x len(m_list) apply() calls, one device->host copy of the results.
@@ -357,7 +361,7 @@ def run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, wo
         for (M, name, k), (_, _, n) in zip(x_shapes, y_shapes):
             x = dev_x[xo:xo + M * k].view(M, k)
             y = method.apply(lay[name], x)
-            if lay[name].mode == "row" and world > 1:
+            if lay[name].mode == "row" and world > 1 and not lay[name].w8a16_reduced:
                 import torch.distributed as dist
                 dist.all_reduce(y)
             dev_y[yo:yo + M * n].view(M, n).copy_(y)
@@ -514,6 +518,8 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only", default=None, metavar="LAYER:M", help="profiling aid: run one dense case only, e.g. gate_up:16 "
                     "(implies --no-extras --no-cpu-baseline, skips the end-to-end leg)")
+    ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: row-parallel all-reduce fused into the GEMM kernel over peer memory (default) or NCCL after it")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays (1 GPU)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup

@@ -101,23 +101,23 @@ int fp8w8a16_linear_noalloc(const uint16_t* x, const uint8_t* w, const void* sca
 /* Row-parallel linear with the tensor-parallel all-reduce fused into the GEMM kernel, over peer memory
  * (NVLink).  Replaces the pair the reference's call site runs per row-parallel layer - apply() on the rank's K
  * shard, then vLLM's tensor_model_parallel_all_reduce of the FP16 [M,N] result (vllm_serve.py:2922-2959) - with one
- * launch per rank: every rank leaves each finished output tile as FP16 in its own communicator buffer, raises a
- * flag in every peer's buffer, and the CTA that finished a tile waits (bounded) for the peers' flags of the same
- * tile, loads their partial tiles and adds them in ascending rank order, so out is bit-identical on all ranks.
+ * launch per rank: the CTA that finishes a piece of an output tile stores its FP16 values, tagged with the launch
+ * number, straight into every peer's inbox, polls (bounded) its own inbox for the peers' values of the same piece
+ * and adds all contributions in ascending rank order, so out is bit-identical on all ranks and the exchange of
+ * early tiles overlaps the math of later ones.
  *
  * A communicator is one device allocation per rank (cudaMalloc at create time; nothing is allocated per call),
  * mapped into the peers through CUDA IPC: create on every rank, exchange the FP8W8A16_COMM_HANDLE_BYTES handles by
  * any host channel, attach every peer, then make the SAME sequence of fp8w8a16_linear_allreduce calls on all ranks
  * (one process per GPU).  fp8w8a16_comm_attach_ptr takes a peer mapping made by other means (cuMem / fabric
  * handles, symmetric-memory allocators) whose layout is another rank's fp8w8a16_comm_base .. + fp8w8a16_comm_bytes.
- * max_out_elems bounds M*N of a call, max_tiles the number of 128-feature x token-tile output tiles;
- * timeout_ms (0 = 2000) bounds every wait for a peer: when it runs out the kernel gives up, out is not written
- * for the affected tiles and fp8w8a16_device_status reports bit 128.  N must be a multiple of 4.
- * Calls are CUDA-graph capturable (launch counting is done on the device). */
+ * max_out_elems bounds M*N of a call (the buffer takes about (10 * world + 2) bytes per element); timeout_ms
+ * (0 = 2000) bounds every wait for a peer: when it runs out the kernel gives up, out is not written for the
+ * affected tiles and fp8w8a16_device_status reports bit 128.  N must be a multiple of 4.
+ * Calls are CUDA-graph capturable (launches are counted on the device). */
 #define FP8W8A16_COMM_HANDLE_BYTES 64
 typedef struct fp8w8a16_comm fp8w8a16_comm;
-int fp8w8a16_comm_create(int rank, int world, int64_t max_out_elems, int max_tiles, unsigned int timeout_ms,
-                         fp8w8a16_comm** comm);
+int fp8w8a16_comm_create(int rank, int world, int64_t max_out_elems, unsigned int timeout_ms, fp8w8a16_comm** comm);
 int fp8w8a16_comm_export(const fp8w8a16_comm* comm, void* handle);
 int fp8w8a16_comm_attach(fp8w8a16_comm* comm, int peer, const void* handle);
 int fp8w8a16_comm_attach_ptr(fp8w8a16_comm* comm, int peer, void* peer_base);

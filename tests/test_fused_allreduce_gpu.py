@@ -15,8 +15,8 @@ def test_wait_for_absent_peer_times_out_and_context_survives(lib):
     ops.device_status()  # clear
     M, N, K = 4, 512, 512
     x, w, s, bh = make_dense(M, N, K, seed=5)
-    a = ops.PeerComm(0, 2, max_out_elems=M * N, max_tiles=64, timeout_ms=50)
-    b = ops.PeerComm(1, 2, max_out_elems=M * N, max_tiles=64, timeout_ms=50)   # stands in for a peer; never launches
+    a = ops.PeerComm(0, 2, max_out_elems=M * N, timeout_ms=50)
+    b = ops.PeerComm(1, 2, max_out_elems=M * N, timeout_ms=50)   # stands in for a peer; never launches
     try:
         assert a.nbytes == b.nbytes and a.base and b.base
         a.attach_ptr(1, b.base)
@@ -40,7 +40,7 @@ def test_fused_allreduce_argument_checks(lib):
         ops.PeerComm(0, 1, max_out_elems=16)            # a world of one has nothing to reduce
     with pytest.raises(RuntimeError):
         ops.PeerComm(3, 2, max_out_elems=16)
-    c = ops.PeerComm(0, 2, max_out_elems=8 * 256, max_tiles=4, timeout_ms=50)
+    c = ops.PeerComm(0, 2, max_out_elems=8 * 256, timeout_ms=50)
     try:
         x, w, s, bh = make_dense(8, 256, 256, seed=6)
         with pytest.raises(RuntimeError, match="not attached"):
@@ -49,8 +49,8 @@ def test_fused_allreduce_argument_checks(lib):
         x2, w2, s2, _ = make_dense(16, 256, 256, seed=7)
         with pytest.raises(RuntimeError, match="exceeds"):
             ops.w8a16_linear_allreduce(c, x2.cuda(), w2.cuda(), s2.cuda(), 256, 256, bh, 128)
-        x3, w3, s3, _ = make_dense(2, 1024, 256, seed=8)
-        with pytest.raises(RuntimeError, match="flag slots"):
-            ops.w8a16_linear_allreduce(c, x3.cuda(), w3.cuda(), s3.cuda(), 1024, 256, bh, 128)
+        x3, w3, s3, _ = make_dense(2, 1022, 256, seed=8)
+        with pytest.raises(RuntimeError, match="multiple of 4"):
+            ops.w8a16_linear_allreduce(c, x3.cuda(), w3.cuda(), s3.cuda(), 1022, 256, bh, 128)
     finally:
         c.close()

@@ -42,7 +42,7 @@ def _worker(rank, world, port, q):
         st = olin.error_stats(y.cpu(), y_ref)
         res["tp_row_allreduce"] = st["rel_rms"] < 1.5e-2 and st["finite"]
         # ---- row-parallel GEMM with the all-reduce fused into the kernel (peer memory) ----
-        comm = par.make_peer_comm(max_out_elems=256 * 5120, max_tiles=2048)
+        comm = par.make_peer_comm(max_out_elems=256 * 5120)
         fused_ok, same_ok = True, True
         cases = [(9, 1024, 512), (1, 5120, 5120), (8, 5120, 5120), (64, 5120, 25600), (200, 1024, 2048), (8, 1000, 1024)]
         for ci, (Mf, Nf, Kf) in enumerate(cases):

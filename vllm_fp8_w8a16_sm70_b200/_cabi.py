@@ -33,7 +33,7 @@ PROTOTYPES = {
     "fp8w8a16_linear": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                 c_void_p, c_size_t, c_void_p]),
     "fp8w8a16_linear_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
-    "fp8w8a16_comm_create": (c_int, [c_int, c_int, c_int64, c_int, ctypes.c_uint, POINTER(c_void_p)]),
+    "fp8w8a16_comm_create": (c_int, [c_int, c_int, c_int64, ctypes.c_uint, POINTER(c_void_p)]),
     "fp8w8a16_comm_export": (c_int, [c_void_p, c_void_p]),
     "fp8w8a16_comm_attach": (c_int, [c_void_p, c_int, c_void_p]),
     "fp8w8a16_comm_attach_ptr": (c_int, [c_void_p, c_int, c_void_p]),

@@ -149,8 +149,6 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
     L.cluster_tiles = tiles;
     if (ar != nullptr && ar->world > 1) {
         W8A16_REQUIRE(N % 4 == 0, FP8W8A16_ERR_UNSUPPORTED, "linear_allreduce: N must be a multiple of 4 (got %d)", N);
-        W8A16_REQUIRE(tiles * kArChunks <= ar->slots, FP8W8A16_ERR_UNSUPPORTED,
-                      "linear_allreduce: %lld output tiles exceed the communicator's %d flag slots", (long long)tiles, ar->slots);
         W8A16_REQUIRE((int64_t)M * N <= ar->part_elems, FP8W8A16_ERR_UNSUPPORTED,
                       "linear_allreduce: M*N = %lld exceeds the communicator's buffer of %lld elements", (long long)M * N,
                       (long long)ar->part_elems);
@@ -250,12 +248,13 @@ MoeLayout moe_layout(int M, int topk, int E, int H, int I) {
 
 
 // ---- peer-memory communicator of the fused row-parallel GEMM + all-reduce ---------------------------------
-// One cudaMalloc per rank with the same layout on every rank: control words, flag array, two partial buffers.
+// One cudaMalloc per rank with the same layout on every rank: control words, the rank's own FP16 staging buffer, and
+// the inbox [2 parities][world sources][part_elems / 2] of 8-byte packets the peers store into.
 struct Comm {
-    int rank, world, slots, device;
+    int rank, world, device;
     unsigned int timeout_ms;
     int64_t part_elems;
-    size_t flags_off, part_off, bytes;
+    size_t part_off, inbox_off, bytes;
     char* base[kArMaxWorld];     // base[rank] is the local allocation, the others are the peers' mappings
     bool ipc_opened[kArMaxWorld];
 };
@@ -265,13 +264,12 @@ int comm_params(const Comm* c, ArParams* ar) {
     ar->world = c->world;
     ar->rank = c->rank;
     ar->timeout_ms = c->timeout_ms;
-    ar->slots = c->slots;
     ar->part_elems = c->part_elems;
     ar->ctrl = reinterpret_cast<unsigned int*>(c->base[c->rank]);
+    ar->part = reinterpret_cast<__half*>(c->base[c->rank] + c->part_off);
     for (int r = 0; r < c->world; ++r) {
         W8A16_REQUIRE(c->base[r] != nullptr, FP8W8A16_ERR_INVALID, "comm: rank %d is not attached", r);
-        ar->flags[r] = reinterpret_cast<unsigned int*>(c->base[r] + c->flags_off);
-        ar->part[r] = reinterpret_cast<__half*>(c->base[r] + c->part_off);
+        ar->inbox[r] = reinterpret_cast<uint2*>(c->base[r] + c->inbox_off);
     }
     return 0;
 }
@@ -470,26 +468,24 @@ struct fp8w8a16_comm {
     w8a16::Comm c;
 };
 
-int fp8w8a16_comm_create(int rank, int world, int64_t max_out_elems, int max_tiles, unsigned int timeout_ms,
-                         fp8w8a16_comm** comm) {
+int fp8w8a16_comm_create(int rank, int world, int64_t max_out_elems, unsigned int timeout_ms, fp8w8a16_comm** comm) {
     W8A16_REQUIRE(comm != nullptr, FP8W8A16_ERR_INVALID, "comm_create: null output pointer");
     *comm = nullptr;
     W8A16_REQUIRE(world >= 2 && world <= kArMaxWorld && rank >= 0 && rank < world, FP8W8A16_ERR_INVALID,
                   "comm_create: rank %d of world %d (2..%d ranks supported)", rank, world, kArMaxWorld);
-    W8A16_REQUIRE(max_out_elems > 0 && max_tiles > 0 && max_tiles <= (1 << 20), FP8W8A16_ERR_INVALID,
-                  "comm_create: max_out_elems=%lld max_tiles=%d", (long long)max_out_elems, max_tiles);
+    W8A16_REQUIRE(max_out_elems > 0 && max_out_elems <= (1ll << 32), FP8W8A16_ERR_INVALID, "comm_create: max_out_elems=%lld",
+                  (long long)max_out_elems);
     fp8w8a16_comm* h = new (std::nothrow) fp8w8a16_comm();
     W8A16_REQUIRE(h != nullptr, FP8W8A16_ERR_CUDA, "comm_create: out of host memory");
     Comm& c = h->c;
     memset(&c, 0, sizeof(c));
     c.rank = rank;
     c.world = world;
-    c.slots = max_tiles * kArChunks;
     c.timeout_ms = timeout_ms ? timeout_ms : 2000u;
     c.part_elems = (max_out_elems + 127) / 128 * 128;
-    c.flags_off = 256;
-    c.part_off = align_up(c.flags_off + (size_t)world * c.slots * sizeof(unsigned int), 256);
-    c.bytes = c.part_off + 2 * (size_t)c.part_elems * sizeof(__half);
+    c.part_off = 256;
+    c.inbox_off = align_up(c.part_off + (size_t)c.part_elems * sizeof(__half), 256);
+    c.bytes = c.inbox_off + 2 * (size_t)world * (size_t)c.part_elems * 4;   // 8 bytes per pair of FP16 values
     cudaError_t e = cudaGetDevice(&c.device);
     void* base = nullptr;
     if (e == cudaSuccess) e = cudaMalloc(&base, c.bytes);

@@ -240,38 +240,15 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
     return v;
 }
 
-// System-scope flag traffic and peer-memory loads of the fused all-reduce.
-__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+// Packets of the fused all-reduce: 16 bytes = two 8-byte halves {2 x FP16, epoch}; 8-byte accesses are single-copy
+// atomic, so a half whose epoch matches carries the data that was stored with it.
+__device__ __forceinline__ void st_packet(uint2* dst, uint32_t d0, uint32_t d1, uint32_t epoch) {
+    asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(dst), "r"(d0), "r"(epoch), "r"(d1), "r"(epoch) : "memory");
 }
-__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint4 ld_packet(const uint2* src) {
+    uint4 v;
+    asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(src) : "memory");
     return v;
-}
-__device__ __forceinline__ uint2 ld_relaxed_sys_u2(const void* p) {
-    uint2 v;
-    asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-    return v;
-}
-// Bounded wait until the flag has reached `epoch` (epochs only grow; a peer may already be one launch ahead).
-__device__ __forceinline__ bool ar_wait_flag(const unsigned int* flag, unsigned int epoch, unsigned int timeout_ms,
-                                             volatile int* dead) {
-    const unsigned long long t0 = globaltimer_ns();
-    const unsigned long long limit = (unsigned long long)timeout_ms * 1000000ull;
-    uint32_t spins = 0;
-    while ((int)(ld_acquire_sys(flag) - epoch) < 0) {
-        if ((++spins & 0xFu) == 0u) {
-            if (*dead) return false;
-            if (globaltimer_ns() - t0 > limit) {
-                *dead = 1;
-                atomicOr(&g_tc_status, 128);
-                return false;
-            }
-            __nanosleep(64);
-        }
-    }
-    return true;
 }
 
 // ---- compile-time configuration ------------------------------------------------------------------
@@ -407,6 +384,80 @@ __device__ __forceinline__ int partial_slot(int c, int tile, int total_kb, int u
     return ((c * units_per_cta) / total_kb == tile) ? 2 * c : 2 * c + 1;
 }
 
+// Exchange of one region of an output tile between the ranks (see ArParams).  `stage` holds this rank's FP16
+// values; every thread handles groups of four consecutive features.  Kept out of line: it runs once per tile and
+// must not cost the main loop registers.
+__device__ __noinline__ void ar_exchange(const ArParams& ar, const __half* stage, uint32_t epoch, int N, int64_t ldo,
+                                         int row_begin, int rows_valid, int n0, int lo, int hi, int td, volatile int* s_dead) {
+    const int64_t box = (int64_t)(epoch & 1u) * ar.world;     // first source slot of this launch's parity
+    const uint2* mine = ar.inbox[ar.rank];
+    // pass 1: push this rank's values of the whole region (posted stores, nothing to wait for)
+    for (int idx4 = lo + td; idx4 < hi; idx4 += kDequantThreads) {
+        const int ml = idx4 >> 5, nl = (idx4 & 31) * 4;
+        if (ml >= rows_valid || n0 + nl >= N) continue;
+        const int64_t off = (int64_t)(row_begin + ml) * ldo + n0 + nl;
+        const uint2 own = *reinterpret_cast<const uint2*>(stage + off);
+        for (int r = 0; r < ar.world; ++r)
+            if (r != ar.rank) st_packet(ar.inbox[r] + ((box + ar.rank) * ar.part_elems + off) / 2, own.x, own.y, epoch);
+    }
+    // pass 2: collect the peers' packets (the first ones cost one NVLink flight, the rest are already there)
+    const unsigned long long limit = (unsigned long long)ar.timeout_ms * 1000000ull;
+    bool dead = false;
+    for (int idx4 = lo + td; idx4 < hi && !dead; idx4 += kDequantThreads) {
+        const int ml = idx4 >> 5, nl = (idx4 & 31) * 4;
+        if (ml >= rows_valid || n0 + nl >= N) continue;
+        const int64_t off = (int64_t)(row_begin + ml) * ldo + n0 + nl;
+        const uint2 own = *reinterpret_cast<const uint2*>(stage + off);
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 1
+        for (int r0 = 0; r0 < ar.world && !dead; r0 += 4) {        // four sources' packets in flight at a time
+            uint4 v[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int r = r0 + q;
+                if (r < ar.world && r != ar.rank) v[q] = ld_packet(mine + ((box + r) * ar.part_elems + off) / 2);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const int r = r0 + q;
+                if (r >= ar.world || dead) continue;
+                uint32_t d0 = own.x, d1 = own.y;
+                if (r != ar.rank) {
+                    if (v[q].y != epoch || v[q].w != epoch) {
+                        const uint2* src = mine + ((box + r) * ar.part_elems + off) / 2;
+                        const unsigned long long t0 = globaltimer_ns();
+                        uint32_t spins = 0;
+                        do {
+                            if ((++spins & 0x1Fu) == 0u) {
+                                if (*s_dead || globaltimer_ns() - t0 > limit) {
+                                    if (!*s_dead) {
+                                        *s_dead = 1;
+                                        atomicOr(&g_tc_status, 128);
+                                    }
+                                    dead = true;
+                                    break;
+                                }
+                            }
+                            v[q] = ld_packet(src);
+                        } while (v[q].y != epoch || v[q].w != epoch);
+                    }
+                    d0 = v[q].x;
+                    d1 = v[q].z;
+                }
+                const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&d0));
+                const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&d1));
+                acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
+            }
+        }
+        if (dead) break;
+        const __half2 o0 = __floats2half2_rn(acc.x, acc.y), o1 = __floats2half2_rn(acc.z, acc.w);
+        uint2 o;
+        o.x = *reinterpret_cast<const uint32_t*>(&o0);
+        o.y = *reinterpret_cast<const uint32_t*>(&o1);
+        *reinterpret_cast<uint2*>(ar.out + off) = o;
+    }
+}
+
 // ---- the kernel --------------------------------------------------------------------------------
 template <int BT, int BK, bool PAIRED, bool AR>
 __global__ void __launch_bounds__(kThreadsTc, TcCfg<BT, BK, PAIRED>::kCtasPerSm)
@@ -531,13 +582,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         set_range();
     }
     const bool has_work = u_begin < u_end;  // uniform for the whole CTA
-    // Fused all-reduce: this launch's epoch (one more than the count of finished fused launches; every rank
-    // makes the same sequence of launches) selects the partial buffer the GEMM result is left in.
+    // Fused all-reduce: this launch's epoch (one more than the count of finished fused launches; every rank makes
+    // the same sequence of launches) tags the packets; the GEMM result itself is first left in a staging buffer.
     unsigned int ar_epoch = 0;
     __half* out_ptr = p.out;
     if (AR) {
         ar_epoch = *reinterpret_cast<volatile unsigned int*>(ar.ctrl) + 1u;
-        out_ptr = ar.part[ar.rank] + (int64_t)(ar_epoch & 1u) * ar.part_elems;
+        out_ptr = ar.part;
     }
 
     if (!has_work) {
@@ -643,55 +694,23 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         (void)tr_i;
         bool ok = true;
 
-        // Fused all-reduce of one finished region of an output tile (16-byte groups [lo, hi) of the BT x 128 tile;
-        // `chunk` tells the regions of a tile apart).  Called by all 256 threads.  This rank's FP16 partial values
-        // are already stored in its partial buffer: publish them (barrier, system-scope fence, one flag per peer),
-        // wait - bounded - for every peer's flag of the same region, then add the peers' values over NVLink in
-        // ascending rank order and store the sum.  A peer's buffer of this parity is not rewritten before this
-        // rank has raised its flags of the NEXT launch, which it does only after finishing this one.
-        auto ar_finish = [&](const Seg& sg, int chunk, int lo, int hi, int dead_in) -> int {
+        // Fused all-reduce of one finished region of an output tile (16-byte groups [lo, hi) of the BT x 128 tile).
+        // Called by all 256 threads.  This rank's FP16 values of the region are already in its staging buffer (written
+        // by this CTA): after a barrier every thread takes four consecutive features, pushes them to every peer's
+        // inbox, then polls - bounded - its own inbox for the peers' packets of the same four features, adds all
+        // contributions in ascending rank order and stores the sum.  The inbox is double-buffered by launch parity: a
+        // peer can be at most one launch ahead, because finishing a launch needs this rank's packets of that launch.
+        auto ar_finish = [&](const Seg& sg, int lo, int hi, int dead_in) -> int {
             if (!AR) return dead_in;
-            const int slot = sg.tile * kArChunks + chunk;
             epi_bar_sync();
-            if (td == 0 && !dead_in) {
-                __threadfence_system();
-                for (int r = 0; r < ar.world; ++r)
-                    if (r != ar.rank) st_release_sys(ar.flags[r] + (int64_t)ar.rank * ar.slots + slot, ar_epoch);
-            }
-            if (td < ar.world && td != ar.rank && !dead_in)
-                ar_wait_flag(ar.flags[ar.rank] + (int64_t)td * ar.slots + slot, ar_epoch, ar.timeout_ms, s_dead);
-            epi_bar_sync();
-            const int dead = dead_in | *s_dead;
-            if (dead) return dead;
+            int dead = dead_in | *s_dead;
             const int n0 = sg.slab * 128;
-            const int64_t par = (int64_t)(ar_epoch & 1u) * ar.part_elems;
-            for (int idx4 = lo + td; idx4 < hi; idx4 += kDequantThreads) {
-                const int ml = idx4 >> 5, nl = (idx4 & 31) * 4;
-                if (ml >= sg.rows_valid || n0 + nl >= p.N) continue;
-                const int64_t off = (int64_t)(sg.row_begin + ml) * p.ldo + n0 + nl;
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 1
-                for (int r0 = 0; r0 < ar.world; r0 += 4) {         // four peers' loads in flight, added in rank order
-                    uint2 v[4];
-#pragma unroll
-                    for (int r = 0; r < 4; ++r)
-                        if (r0 + r < ar.world) v[r] = ld_relaxed_sys_u2(ar.part[r0 + r] + par + off);
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) {
-                        if (r0 + r < ar.world) {
-                            const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&v[r].x));
-                            const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&v[r].y));
-                            acc.x += a.x; acc.y += a.y; acc.z += b.x; acc.w += b.y;
-                        }
-                    }
-                }
-                const __half2 o0 = __floats2half2_rn(acc.x, acc.y), o1 = __floats2half2_rn(acc.z, acc.w);
-                uint2 o;
-                o.x = *reinterpret_cast<const uint32_t*>(&o0);
-                o.y = *reinterpret_cast<const uint32_t*>(&o1);
-                *reinterpret_cast<uint2*>(ar.out + off) = o;
-            }
-            return dead;
+            if (!dead) ar_exchange(ar, out_ptr, ar_epoch, p.N, p.ldo, sg.row_begin, sg.rows_valid, n0, lo, hi, td, s_dead);
+            // one verdict for the whole CTA, published by one thread between two barriers taken by all
+            epi_bar_sync();
+            if (td == 0) s_ticket[1] = *s_dead;
+            epi_bar_sync();
+            return dead_in | s_ticket[1];
         };
 
         // Epilogue of one finished segment: TMEM -> registers -> FP16 output, or fp32 partial tile + ticket
@@ -803,9 +822,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     if (n + 3 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 3, g.w, uu.w);
                 }
                 if (td == 0) p.tickets[sg.tile] = 0u;  // leave the counter clean for the next launch
-                if (AR) return ar_finish(sg, 0, 0, BT * 32, dead_now);
+                if (AR) return ar_finish(sg, 0, BT * 32, dead_now);
             }
-            if (AR && direct) return ar_finish(sg, 0, 0, BT * 32, dead_now);
+            if (AR && direct) return ar_finish(sg, 0, BT * 32, dead_now);
             return dead_now;
         };
 
@@ -946,7 +965,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rnk));
                 const int chunk = (BT * 32 + p.cluster_size - 1) / p.cluster_size;
                 const int lo = (int)rnk * chunk, hi = min(BT * 32, lo + chunk);
-                if (lo < hi) stop = ar_finish(last_sg, (int)rnk, lo, hi, stop);
+                if (lo < hi) stop = ar_finish(last_sg, lo, hi, stop);
             }
         }
     }

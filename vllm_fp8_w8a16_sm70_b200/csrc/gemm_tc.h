@@ -39,19 +39,19 @@ struct TcParams {
 };
 
 // Fused all-reduce of a row-parallel GEMM over peer memory (one process per GPU, buffers mapped through CUDA IPC).
-// Every rank runs the same launch.  A finished output tile is left as FP16 in the rank's own partial buffer, a flag is
-// stored into every peer's flag array, and the CTA that finished the tile waits for the peers' flags of the SAME tile,
-// loads their partial tiles over NVLink and adds them in ascending rank order (identical result on every rank).
+// Every rank runs the same launch.  The CTA that finishes a region of an output tile pushes its FP16 values into every
+// peer's inbox as 8-byte packets {two FP16 values, launch epoch} (posted NVLink stores; the epoch in every packet is
+// the arrival flag, so no fence and no separate flag is needed), then polls its OWN inbox for the peers' packets of
+// the same region and adds all contributions in ascending rank order: the result is identical on every rank, and the
+// exchange of early tiles overlaps the math of later ones.
 constexpr int kArMaxWorld = 8;
-constexpr int kArChunks = 8;          // flag slots per output tile (one per CTA of a split-K cluster)
 struct ArParams {
     int world;                        // 0 = not fused
     int rank;
-    unsigned int timeout_ms;          // bound of the wait for a peer's flag
-    int slots;                        // flag slots per source rank
+    unsigned int timeout_ms;          // bound of the wait for a peer's packets
     unsigned int* ctrl;               // local: [0] = number of finished fused launches (epoch), [1] = CTAs done in this launch
-    unsigned int* flags[kArMaxWorld]; // flags[r]: rank r's flag array [world][slots] (entry [s][i]: epoch of source s, slot i)
-    __half* part[kArMaxWorld];        // part[r]: rank r's partial buffers [2][part_elems] (parity = epoch & 1)
+    __half* part;                     // local FP16 staging of this rank's own result [part_elems]
+    uint2* inbox[kArMaxWorld];        // inbox[r]: rank r's inbox [2 parities][world sources][part_elems / 2] packets
     int64_t part_elems;
     __half* out;                      // reduced output [M, N] (local)
 };

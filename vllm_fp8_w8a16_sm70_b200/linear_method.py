@@ -44,7 +44,18 @@ def _apply_2d(layer, x: torch.Tensor, bias, N: int, K: int, scale: torch.Tensor,
     if x2d.dtype != torch.float16:
         x2d = x2d.to(torch.float16)
     x2d = x2d.contiguous()
-    out = ops.w8a16_linear(x2d, layer.weight, scale, N, K, block_h, 128)
+    # A row-parallel layer that carries a peer-memory communicator (``layer.w8a16_peer_comm``, set by the integrator
+    # together with ``reduce_results = False``) gets its tensor-parallel all-reduce done inside the GEMM kernel; a
+    # bias would have to be added on one rank only before the reduce (vllm_serve.py:2937-2945), so such calls and
+    # calls larger than the communicator's buffer take the plain path and the caller's own all-reduce.
+    comm = getattr(layer, "w8a16_peer_comm", None)
+    if comm is not None and bias is None and x2d.shape[0] * N <= getattr(comm, "max_out_elems", 0):
+        out = ops.w8a16_linear_allreduce(comm, x2d, layer.weight, scale, N, K, block_h, 128)
+        layer.w8a16_reduced = True      # tells the caller that this result is already summed over the ranks
+    else:
+        out = ops.w8a16_linear(x2d, layer.weight, scale, N, K, block_h, 128)
+        if comm is not None:
+            layer.w8a16_reduced = False
     out = out.reshape(orig_shape[:-1] + (N,))
     if bias is not None:
         out = out + bias.to(out.dtype)

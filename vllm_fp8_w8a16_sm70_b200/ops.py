@@ -198,21 +198,21 @@ def w8a16_linear_noalloc(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor,
 # row-parallel linear with the all-reduce fused into the GEMM kernel (peer memory over NVLink)
 # ------------------------------------------------------------------------------------------------
 class PeerComm:
-    """One rank's end of the peer-memory communicator (``fp8w8a16_comm_*``): a device buffer (flags + two FP16
-    partial buffers) that the other ranks' GPUs map through CUDA IPC.  ``handle()`` is the 64-byte IPC handle to send
+    """One rank's end of the peer-memory communicator (``fp8w8a16_comm_*``): a device buffer (FP16 staging +
+    a double-buffered inbox of tagged packets) that the other ranks' GPUs map through CUDA IPC.  ``handle()`` is the 64-byte IPC handle to send
     to the peers by any host channel; ``attach(peer, handle)`` maps a peer's buffer.  All ranks must then make the
     same sequence of ``w8a16_linear_allreduce`` calls."""
 
-    def __init__(self, rank: int, world: int, max_out_elems: int, max_tiles: int = 4096, timeout_ms: int = 2000,
+    def __init__(self, rank: int, world: int, max_out_elems: int, timeout_ms: int = 2000,
                  device: Optional[torch.device] = None):
         import ctypes
-        self.rank, self.world = rank, world
+        self.rank, self.world, self.max_out_elems = rank, world, max_out_elems
         self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         if self.device.type != "cuda":
             raise RuntimeError("PeerComm needs a CUDA device (there is no CPU path)")
         self._h = ctypes.c_void_p()
         with _dev_guard(self.device):
-            _cabi.check(_cabi.load().fp8w8a16_comm_create(rank, world, max_out_elems, max_tiles, timeout_ms,
+            _cabi.check(_cabi.load().fp8w8a16_comm_create(rank, world, max_out_elems, timeout_ms,
                                                          ctypes.byref(self._h)), "fp8w8a16_comm_create")
 
     def handle(self) -> bytes:

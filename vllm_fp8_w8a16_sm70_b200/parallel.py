@@ -81,14 +81,12 @@ class TensorParallelLinear:
         return getattr(self.comm, "max_out_elems", 0)
 
 
-def make_peer_comm(max_out_elems: int, max_tiles: int = 4096, timeout_ms: int = 2000,
-                   group: Optional[dist.ProcessGroup] = None) -> "ops.PeerComm":
+def make_peer_comm(max_out_elems: int, timeout_ms: int = 2000, group: Optional[dist.ProcessGroup] = None) -> "ops.PeerComm":
     """Collective: every rank of ``group`` creates its communicator buffer on its current CUDA device, the IPC handles
     travel through ``all_gather_object`` and every rank maps every peer.  Ends with a barrier so that no rank launches
     before all mappings exist."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
-    comm = ops.PeerComm(rank, world, max_out_elems, max_tiles, timeout_ms)
-    comm.max_out_elems = max_out_elems
+    comm = ops.PeerComm(rank, world, max_out_elems, timeout_ms)
     handles = [None] * world
     dist.all_gather_object(handles, comm.handle(), group=group)
     for peer, h in enumerate(handles):
