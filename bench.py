@@ -196,7 +196,12 @@ class DenseStack:
         self.copies = {}
         # row-parallel layers: all-reduce fused into the GEMM kernel over peer memory for up to 256 tokens
         # (larger batches, and --allreduce nccl, use NCCL after the GEMM)
-        self.comm = par.make_peer_comm(max_out_elems=256 * 5120) if (world > 1 and fused) else None
+        self.comm = None
+        if world > 1 and fused:
+            try:   # make_peer_comm raises on every rank or on none
+                self.comm = par.make_peer_comm(max_out_elems=256 * 5120)
+            except RuntimeError as exc:
+                print(f"[bench] rank {rank}: {exc}; measuring the NCCL all-reduce instead", file=sys.stderr)
         for si, (name, N, K, mode) in enumerate(DENSE_SHAPES):
             n = max(2, min(max_copies, -(-min_bytes // (N * K // world))))
             lst = []

@@ -63,7 +63,22 @@ def _ep_worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("worker", [_tp_worker, _ep_worker])
+def _comm_failure_worker(rank, world, port, q):
+    """Without a GPU no rank can create its communicator buffer: every rank must raise (none may hang in a
+    collective waiting for the others), and a row-parallel layer without a communicator keeps the NCCL/gloo path."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from vllm_fp8_w8a16_sm70_b200 import parallel as par
+    try:
+        par.make_peer_comm(max_out_elems=1024, timeout_ms=50)
+        ok = False
+    except RuntimeError as exc:
+        ok = "could not be set up" in str(exc)
+    q.put((rank, ok))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("worker", [_tp_worker, _ep_worker, _comm_failure_worker])
 def test_two_gloo_ranks(worker):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()

@@ -720,7 +720,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         auto epilogue = [&](const Seg& sg, int si) -> int {
             const int n0 = sg.slab * 128;
             const uint32_t t_acc = t_lane + (uint32_t)((si % C::kAccBufs) * C::kAccCols);
+            if (td == 0) TC_TRACE(0, 200, 0);
             if (ok) ok = mbar_wait(bar_acc + 8 * (si % C::kAccBufs), (uint32_t)(si / C::kAccBufs) & 1u, s_dead, 64);
+            if (td == 0) TC_TRACE(0, 200, 1);
             ok = __all_sync(0xFFFFFFFFu, ok) != 0;  // tcgen05.ld is warp-collective: keep the warp together
             const bool clustered = p.cluster_size > 1;
             const bool direct = !clustered && (sg.n_contrib == 1);
@@ -766,6 +768,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     }
                 }
             }
+            if (td == 0) TC_TRACE(0, 200, 2);
             tc_fence_before();
             // Hand-off.  All 256 threads take both barriers in every segment, whatever happened above,
             // and act only on values that thread 0 publishes between them, so that a timed-out wait
@@ -925,7 +928,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         if (!stop && pend_i >= 0) stop = epilogue(pend, pend_i);
         if (p.cluster_size > 1) {
             // every CTA of the cluster has parked its fp32 partial tile in its own shared memory
+            if (td == 0) TC_TRACE(0, 200, 3);
             cluster_sync_all();
+            if (td == 0) TC_TRACE(0, 200, 4);
             if (!stop) {
                 Seg last_sg;   // the one segment of this CTA
                 get_seg<BT>(p, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
@@ -957,7 +962,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     if (n + 3 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 3, g.w, uu.w);
                 }
             }
+            if (td == 0) TC_TRACE(0, 200, 5);
             cluster_sync_all();   // nobody leaves (and frees its shared memory) while a peer may still read it
+            if (td == 0) TC_TRACE(0, 201, 0);
             if (AR) {
                 Seg last_sg;
                 get_seg<BT>(p, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);

@@ -83,15 +83,32 @@ class TensorParallelLinear:
 
 def make_peer_comm(max_out_elems: int, timeout_ms: int = 2000, group: Optional[dist.ProcessGroup] = None) -> "ops.PeerComm":
     """Collective: every rank of ``group`` creates its communicator buffer on its current CUDA device, the IPC handles
-    travel through ``all_gather_object`` and every rank maps every peer.  Ends with a barrier so that no rank launches
-    before all mappings exist."""
+    travel through ``all_gather_object`` and every rank maps every peer.  Failures are agreed on: if any rank cannot
+    create or map a buffer, every rank closes what it has and raises, so the callers stay in step.  Ends with a
+    barrier so that no rank launches before all mappings exist."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
-    comm = ops.PeerComm(rank, world, max_out_elems, timeout_ms)
+    comm, err = None, None
+    try:
+        comm = ops.PeerComm(rank, world, max_out_elems, timeout_ms)
+        mine = comm.handle()
+    except Exception as exc:  # noqa: BLE001 - re-raised on every rank below
+        mine, err = None, repr(exc)
     handles = [None] * world
-    dist.all_gather_object(handles, comm.handle(), group=group)
-    for peer, h in enumerate(handles):
-        if peer != rank:
-            comm.attach(peer, h)
+    dist.all_gather_object(handles, (mine, err), group=group)
+    if all(h is not None for h, _ in handles):
+        try:
+            for peer, (h, _) in enumerate(handles):
+                if peer != rank:
+                    comm.attach(peer, h)
+        except Exception as exc:  # noqa: BLE001
+            err = repr(exc)
+    verdicts = [None] * world
+    dist.all_gather_object(verdicts, err, group=group)
+    failed = [(r, e) for r, ((h, e0), e) in enumerate(zip(handles, verdicts)) if h is None or e is not None]
+    if failed:
+        if comm is not None:
+            comm.close()
+        raise RuntimeError(f"peer-memory communicator could not be set up: {failed}")
     dist.barrier(group=group)
     return comm
 
