@@ -112,3 +112,37 @@ def test_moe_method_apply(lib):
     lay.activation = "relu"
     with pytest.raises(NotImplementedError):
         m.apply(lay, xb, d["tw"].cuda(), d["ids"].cuda(), None)
+
+
+def test_checkpoint_to_module_and_moe(lib, tmp_path):
+    """File -> loader -> engine: a fused QKV read from a safetensors file, and an expert stack fed to the MoE layer."""
+    st = pytest.importorskip("safetensors.torch")
+    from oracle import linear as olin, moe as omoe
+    from vllm_fp8_w8a16_sm70_b200 import checkpoint as ck, ops
+    g = torch.Generator().manual_seed(3)
+    tensors = {}
+    for i, (nm, n) in enumerate((("q_proj", 512), ("k_proj", 128), ("v_proj", 128))):
+        q8, s = olin.quantize_block_fp8(torch.randn(n, 384, generator=g) * 0.02)
+        tensors[f"a.{nm}.weight"] = q8.view(torch.float8_e4m3fn)
+        tensors[f"a.{nm}.weight_scale_inv"] = s.to(torch.bfloat16)
+    E, I, H, topk, M = 4, 128, 256, 2, 5
+    for e in range(E):
+        for nm, (n, k) in (("gate_proj", (I, H)), ("up_proj", (I, H)), ("down_proj", (H, I))):
+            q8, s = olin.quantize_block_fp8(torch.randn(n, k, generator=g) * 0.05)
+            tensors[f"m.experts.{e}.{nm}.weight"] = q8.view(torch.float8_e4m3fn)
+            tensors[f"m.experts.{e}.{nm}.weight_scale_inv"] = s.to(torch.bfloat16)
+    f = tmp_path / "ckpt.safetensors"
+    st.save_file(tensors, str(f))
+    qkv = ck.load_fused(f, ["a.q_proj", "a.k_proj", "a.v_proj"])
+    mod = ck.to_linear_module(qkv)
+    x = torch.randn(7, 384, generator=g).to(torch.float16)
+    y = mod(x.cuda())
+    stt = olin.error_stats(y.cpu(), olin.oracle_linear_fp32(x, qkv.weight, qkv.scale, 128))
+    assert stt["rel_rms"] < 1e-2 and stt["finite"]
+    ex = ck.load_experts(f, "m.experts")
+    xm = torch.randn(M, H, generator=g).to(torch.float16)
+    ids = torch.stack([torch.randperm(E, generator=g)[:topk] for _ in range(M)]).to(torch.int32)
+    tw = torch.softmax(torch.randn(M, topk, generator=g), -1)
+    d = ex.to("cuda")
+    out = ops.moe_forward(xm.cuda(), tw.cuda(), ids.cuda(), d.w13, d.s13, d.w2, d.s2, block_h=d.block_h)
+    omoe.check_moe(out.cpu(), omoe.moe_reference_fp32(xm, tw, ids, ex.w13, ex.s13, ex.w2, ex.s2))

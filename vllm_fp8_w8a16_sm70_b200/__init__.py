@@ -6,6 +6,7 @@ the Python layer mirrors the vLLM-facing hooks of KumphanartDansiri/vllm-fp8-w8a
 
 from .backend import backend_mode, select_backend  # noqa: F401
 from . import ops  # noqa: F401
+from . import checkpoint  # noqa: F401
 from .linear_method import CompressedTensorsW8A16Fp8, Fp8LinearMethod  # noqa: F401
 from .module import FP8W8A16Linear  # noqa: F401
 from .moe_method import CompressedTensorsFp8MoEMethod, Fp8MoEMethod  # noqa: F401
