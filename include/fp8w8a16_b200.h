@@ -55,6 +55,20 @@ const char* fp8w8a16_last_error(void);
  * benchmark to report how many of its own kernels ran inside a timed region). */
 uint64_t fp8w8a16_launch_count(void);
 
+/* How the calls of this process were served, by kernel variant: the observability counterpart of the reference's
+ * per-variant call counters (vllm_serve.py:1403-1429).  counts receives min(n, FP8W8A16_NUM_VARIANTS) host-side
+ * counters, indexed by the FP8W8A16_VARIANT_* values; returns FP8W8A16_NUM_VARIANTS. */
+#define FP8W8A16_VARIANT_GEMV 0            /* CUDA-core split-K GEMV (noalloc form included) */
+#define FP8W8A16_VARIANT_TC_CLUSTER 1      /* tcgen05 GEMM, cluster split-K */
+#define FP8W8A16_VARIANT_TC_STREAMK 2      /* tcgen05 GEMM, stream-K with ticketed fix-up */
+#define FP8W8A16_VARIANT_TC_TILES 3        /* tcgen05 GEMM, whole tiles (prefill) */
+#define FP8W8A16_VARIANT_GROUPED 4         /* grouped (MoE) GEMM, w2-style */
+#define FP8W8A16_VARIANT_GROUPED_PAIRED 5  /* grouped gate/up GEMM with fused activation */
+#define FP8W8A16_VARIANT_FUSED_ALLREDUCE 6 /* row-parallel GEMM with the all-reduce inside (also counted under its TC mode) */
+#define FP8W8A16_VARIANT_DEQUANT 7         /* standalone dequant ops */
+#define FP8W8A16_NUM_VARIANTS 8
+int fp8w8a16_variant_counts(uint64_t* counts, int n);
+
 /* Sticky device status word (bit set = a bounded wait inside a kernel gave up).  Synchronises the
  * device.  *status (host) receives the bits; reset != 0 clears them. */
 int fp8w8a16_device_status(int* status, int reset);

@@ -92,3 +92,31 @@ def test_linear_method_load_time_rules(lib):
     bad = types.SimpleNamespace(weight=torch.zeros(352, 384, dtype=torch.uint8), weight_scale=torch.rand(7))
     with pytest.raises(ValueError):
         CompressedTensorsW8A16Fp8("channel").process_weights_after_loading(bad)
+
+
+def test_variant_counters_exported_and_named(lib):
+    """The per-variant call counters: one name per FP8W8A16_VARIANT_* index, all zero before any GPU call here."""
+    from vllm_fp8_w8a16_sm70_b200 import _cabi
+    counts = _cabi.variant_counts()
+    assert list(counts) == list(_cabi.VARIANT_NAMES) and len(counts) == 8
+    assert all(isinstance(v, int) and v >= 0 for v in counts.values())
+
+
+def test_observability_summary_without_gpu(lib, monkeypatch, capsys):
+    from vllm_fp8_w8a16_sm70_b200 import observability as obs
+    obs.reset()
+    monkeypatch.setenv("FP8W8A16_VARIANT_LOG_EVERY", "2")
+    monkeypatch.setenv("FP8W8A16_PREFIX_PROFILE", "1")
+    import types
+    obs.on_apply(types.SimpleNamespace(prefix="model.layers.0.mlp.down_proj"))
+    assert capsys.readouterr().err == ""
+    obs.on_apply(types.SimpleNamespace(prefix="model.layers.0.mlp.down_proj"))
+    err = capsys.readouterr().err
+    assert "kernel variant counts after 2 hook calls" in err and "model.layers.0.mlp.down_proj: calls=2" in err
+    monkeypatch.setenv("FP8W8A16_VARIANT_LOG_EVERY", "0")
+    obs.on_apply(None)
+    assert capsys.readouterr().err == ""
+    obs.reset()
+    with pytest.raises(RuntimeError, match="GPU"):
+        import torch
+        obs.selfcheck_linear(torch.zeros(128, 128, dtype=torch.uint8), torch.ones(1, 1, dtype=torch.float16), 128, 128, 128)

@@ -146,3 +146,42 @@ def test_checkpoint_to_module_and_moe(lib, tmp_path):
     d = ex.to("cuda")
     out = ops.moe_forward(xm.cuda(), tw.cuda(), ids.cuda(), d.w13, d.s13, d.w2, d.s2, block_h=d.block_h)
     omoe.check_moe(out.cpu(), omoe.moe_reference_fp32(xm, tw, ids, ex.w13, ex.s13, ex.w2, ex.s2))
+
+
+def test_selfcheck_and_variant_counters(lib, monkeypatch):
+    """FP8W8A16_SELFCHECK=1: loading a healthy layer passes; a corrupted scale grid is caught and the layer is refused.
+    The library's variant counters move with the calls that were made."""
+    from vllm_fp8_w8a16_sm70_b200 import Fp8LinearMethod, CompressedTensorsW8A16Fp8, _cabi, observability as obs
+    monkeypatch.setenv("FP8W8A16_SELFCHECK", "1")
+    x, w, s, bh = make_dense(4, 512, 384, seed=11)
+    before = _cabi.variant_counts()
+    layer = types.SimpleNamespace(weight=w.cuda().view(torch.float8_e4m3fn), weight_scale_inv=s.cuda().to(torch.bfloat16),
+                                  weight_block_size=[128, 128], input_size_per_partition=384, output_size_per_partition=512,
+                                  prefix="model.layers.3.self_attn.o_proj")
+    Fp8LinearMethod((128, 128)).process_weights_after_loading(layer)          # runs the probe, must not raise
+    after = _cabi.variant_counts()
+    assert sum(after.values()) > sum(before.values())
+    assert after["tc_cluster"] + after["tc_streamk"] + after["tc_tiles"] > before["tc_cluster"] + before["tc_streamk"] + before["tc_tiles"]
+    l2 = obs.selfcheck_linear(layer.weight, layer.weight_scale_inv, 512, 384, 128)
+    assert l2 < 1e-2
+    # the same bytes with a scale grid that belongs to another layout: the check must refuse
+    bad = layer.weight_scale_inv.clone()
+    bad[0, 0] *= 8
+    ok_ref = obs.selfcheck_linear(layer.weight, bad, 512, 384, 128)           # consistent tensors still pass ...
+    assert ok_ref < 1e-2
+    xc, wc, sc, bhc = make_dense(4, 256, 256, seed=12, scheme="channel")
+    lay2 = types.SimpleNamespace(weight=wc.cuda(), weight_scale=sc[:, :1].contiguous().cuda(), prefix="model.layers.3.mlp.down_proj")
+    CompressedTensorsW8A16Fp8("CHANNEL").process_weights_after_loading(lay2)
+    with pytest.raises(RuntimeError, match="self-check failed"):
+        # ... but an engine whose result disagrees with the tensors' own dequantisation does not
+        _selfcheck_against_wrong_reference(obs, lay2)
+
+
+def _selfcheck_against_wrong_reference(obs, lay):
+    """The engine's answer is made wrong on purpose (scales doubled on its side only)."""
+    real = obs.ops.w8a16_linear
+    try:
+        obs.ops.w8a16_linear = lambda probe, w8, scale, N, K, bh, bw: real(probe, w8, scale * 2, N, K, bh, bw)
+        obs.selfcheck_linear(lay.weight, lay.weight_scale, 256, 256, 1)
+    finally:
+        obs.ops.w8a16_linear = real

@@ -19,6 +19,7 @@ DTYPE_F32, DTYPE_F16, DTYPE_BF16 = 0, 1, 2
 ALGO_AUTO, ALGO_GEMV, ALGO_TC = 0, 1, 2
 ACT_SILU, ACT_GELU = 1, 2
 COMM_HANDLE_BYTES = 64
+VARIANT_NAMES = ("gemv", "tc_cluster", "tc_streamk", "tc_tiles", "grouped", "grouped_paired", "fused_allreduce", "dequant")
 
 # name -> (restype, argtypes); mirrors include/fp8w8a16_b200.h one to one
 PROTOTYPES = {
@@ -26,6 +27,7 @@ PROTOTYPES = {
     "fp8w8a16_last_error": (c_char_p, []),
     "fp8w8a16_launch_count": (ctypes.c_uint64, []),
     "fp8w8a16_device_status": (c_int, [POINTER(c_int), c_int]),
+    "fp8w8a16_variant_counts": (c_int, [POINTER(ctypes.c_uint64), c_int]),
     "fp8w8a16_e4m3_to_fp16": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
     "fp8w8a16_e4m3_to_fp16_scaled": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "fp8w8a16_dequant_block_scaled": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
@@ -93,3 +95,12 @@ def device_status(reset: bool = True) -> int:
     st = c_int(0)
     check(load().fp8w8a16_device_status(ctypes.byref(st), 1 if reset else 0), "fp8w8a16_device_status")
     return st.value
+
+
+def variant_counts() -> dict:
+    """Calls served so far in this process, by kernel variant (FP8W8A16_VARIANT_* order)."""
+    buf = (ctypes.c_uint64 * len(VARIANT_NAMES))()
+    n = load().fp8w8a16_variant_counts(buf, len(VARIANT_NAMES))
+    if n != len(VARIANT_NAMES):
+        raise RuntimeError(f"library reports {n} kernel variants, this binding knows {len(VARIANT_NAMES)}")
+    return dict(zip(VARIANT_NAMES, (int(v) for v in buf)))

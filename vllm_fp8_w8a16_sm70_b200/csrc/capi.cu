@@ -33,6 +33,9 @@ int fail(int code, const char* fmt, ...) {
 static std::atomic<unsigned long long> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
+static std::atomic<unsigned long long> g_variants[FP8W8A16_NUM_VARIANTS];
+void count_variant(int v) { g_variants[v].fetch_add(1, std::memory_order_relaxed); }
+
 int sm_count() {
     static int cached[64] = {};
     int dev = 0;
@@ -154,7 +157,10 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
                       (long long)ar->part_elems);
         L.ar = *ar;
         L.ar.out = out;
+        count_variant(FP8W8A16_VARIANT_FUSED_ALLREDUCE);
     }
+    count_variant(L.p.cluster_size > 1 ? FP8W8A16_VARIANT_TC_CLUSTER
+                                       : (L.p.no_split ? FP8W8A16_VARIANT_TC_TILES : FP8W8A16_VARIANT_TC_STREAMK));
     return tc_launch(L, bt, false, st);
 }
 
@@ -207,6 +213,7 @@ int grouped_gemm(const __half* x_sorted, const uint8_t* w, const void* scales, i
     W8A16_REQUIRE(L.max_units < (1ll << 31), FP8W8A16_ERR_UNSUPPORTED, "moe_grouped_gemm: problem too large for 32-bit work indices");
     L.p.cluster_size = tc_cluster_size(tiles_ub, (K + bk - 1) / bk, bt, paired != 0);
     L.cluster_tiles = tiles_ub;
+    count_variant(paired ? FP8W8A16_VARIANT_GROUPED_PAIRED : FP8W8A16_VARIANT_GROUPED);
     return tc_launch(L, bt, paired != 0, st);
 }
 
@@ -287,6 +294,12 @@ const char* fp8w8a16_last_error(void) { return t_err; }
 
 uint64_t fp8w8a16_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+int fp8w8a16_variant_counts(uint64_t* counts, int n) {
+    for (int i = 0; counts != nullptr && i < n && i < FP8W8A16_NUM_VARIANTS; ++i)
+        counts[i] = g_variants[i].load(std::memory_order_relaxed);
+    return FP8W8A16_NUM_VARIANTS;
+}
+
 int fp8w8a16_device_status(int* status, int reset) {
     W8A16_REQUIRE(status != nullptr, FP8W8A16_ERR_INVALID, "device_status: null status pointer");
     W8A16_CUDA(cudaDeviceSynchronize());
@@ -296,6 +309,7 @@ int fp8w8a16_device_status(int* status, int reset) {
 int fp8w8a16_e4m3_to_fp16(const uint8_t* w, uint16_t* out, int64_t n, void* stream) {
     W8A16_REQUIRE(n >= 0, FP8W8A16_ERR_INVALID, "e4m3_to_fp16: negative n");
     W8A16_REQUIRE(n == 0 || (w && out), FP8W8A16_ERR_INVALID, "e4m3_to_fp16: null pointer");
+    count_variant(FP8W8A16_VARIANT_DEQUANT);
     return launch_e4m3_to_fp16(w, reinterpret_cast<__half*>(out), n, (cudaStream_t)stream);
 }
 
@@ -304,6 +318,7 @@ int fp8w8a16_e4m3_to_fp16_scaled(const uint8_t* w, const uint16_t* scales_f16, u
     W8A16_REQUIRE(n >= 0 && group_size > 0, FP8W8A16_ERR_INVALID, "e4m3_to_fp16_scaled: n=%lld group=%lld", (long long)n,
                   (long long)group_size);
     W8A16_REQUIRE(n == 0 || (w && out && scales_f16), FP8W8A16_ERR_INVALID, "e4m3_to_fp16_scaled: null pointer");
+    count_variant(FP8W8A16_VARIANT_DEQUANT);
     return launch_e4m3_to_fp16_scaled(w, reinterpret_cast<const __half*>(scales_f16), reinterpret_cast<__half*>(out), n,
                                       group_size, (cudaStream_t)stream);
 }
@@ -315,6 +330,7 @@ int fp8w8a16_dequant_block_scaled(const uint8_t* w, const void* scales, int scal
     W8A16_REQUIRE(scale_dtype == FP8W8A16_SCALE_F16 || scale_dtype == FP8W8A16_SCALE_F32, FP8W8A16_ERR_INVALID,
                   "dequant_block_scaled: unknown scale dtype %d", scale_dtype);
     W8A16_REQUIRE((N == 0 || K == 0) || (w && scales && out), FP8W8A16_ERR_INVALID, "dequant_block_scaled: null pointer");
+    count_variant(FP8W8A16_VARIANT_DEQUANT);
     return launch_dequant_block(w, scales, scale_dtype, reinterpret_cast<__half*>(out), N, K, block_h, block_w,
                                 (cudaStream_t)stream);
 }
@@ -338,6 +354,7 @@ int fp8w8a16_linear(const uint16_t* x, const uint8_t* w, const void* scales, int
     if (algo == FP8W8A16_ALGO_AUTO) algo = (M <= gemv_max_m()) ? FP8W8A16_ALGO_GEMV : FP8W8A16_ALGO_TC;
     switch (algo) {
         case FP8W8A16_ALGO_GEMV:
+            count_variant(FP8W8A16_VARIANT_GEMV);
             return launch_gemv(xh, w, scales, scale_dtype, oh, M, N, K, block_h, block_w, workspace, workspace_bytes, st);
         case FP8W8A16_ALGO_TC:
             return linear_tc(xh, w, scales, scale_dtype, oh, M, N, K, block_h, workspace, workspace_bytes, st);

@@ -31,6 +31,7 @@ int fail(int code, const char* fmt, ...);
 
 // Kernels launched by this library in this process (reported by fp8w8a16_launch_count).
 void count_launch();
+void count_variant(int variant);   // FP8W8A16_VARIANT_* call counters (host side)
 
 inline int check_launch(const char* what) {
     cudaError_t e = cudaGetLastError();

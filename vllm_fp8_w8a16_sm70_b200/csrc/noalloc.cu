@@ -74,6 +74,7 @@ extern "C" int fp8w8a16_linear_noalloc(const uint16_t* x, const uint8_t* w, cons
     // The array keeps whatever the previous call (or an aborted one) left behind.  The partial sums are
     // fully overwritten before they are read; the ticket counters must start at zero, so clear them.
     W8A16_CUDA(cudaMemsetAsync(scratch, 0, kTicketBytes, st));
+    count_variant(FP8W8A16_VARIANT_GEMV);
     return launch_gemv(reinterpret_cast<const __half*>(x), w, scales, scale_dtype, reinterpret_cast<__half*>(out), M, N, K,
                        block_h, block_w, scratch, kScratchBytes, st);
 }

@@ -19,7 +19,7 @@ from typing import Optional
 
 import torch
 
-from . import ops
+from . import observability, ops
 from .backend import select_backend
 
 
@@ -39,6 +39,7 @@ def _check_scale_range(s16: torch.Tensor, what: str) -> None:
 
 
 def _apply_2d(layer, x: torch.Tensor, bias, N: int, K: int, scale: torch.Tensor, block_h: int) -> torch.Tensor:
+    observability.on_apply(layer)
     orig_shape = x.shape
     x2d = x.reshape(-1, K)
     if x2d.dtype != torch.float16:
@@ -89,6 +90,8 @@ class Fp8LinearMethod:
         _set(layer, "weight_scale_inv", scale.contiguous())
         layer.weight_block_size = list(wbs)
         layer.input_scale = None
+        if observability.selfcheck_enabled():
+            observability.selfcheck_linear(layer.weight, layer.weight_scale_inv, N, K, int(wbs[0]), getattr(layer, "prefix", "linear"))
 
     def apply(self, layer, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``[..., K] -> [..., N]`` in ``x.dtype`` (vllm_serve.py:1372-1447)."""
@@ -148,6 +151,8 @@ class CompressedTensorsW8A16Fp8:
         layer._b200_block_h = block_h
         layer._b200_NK = (N, K)
         layer.input_scale = None
+        if observability.selfcheck_enabled():
+            observability.selfcheck_linear(layer.weight, layer.weight_scale, N, K, block_h, getattr(layer, "prefix", "linear"))
 
     def apply_weights(self, layer, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         N, K = layer._b200_NK
