@@ -185,3 +185,24 @@ def _selfcheck_against_wrong_reference(obs, lay):
         obs.selfcheck_linear(lay.weight, lay.weight_scale, 256, 256, 1)
     finally:
         obs.ops.w8a16_linear = real
+
+
+def test_compiled_hook_matches_eager(lib):
+    """torch.compile (graph capture only, no codegen) of a function that calls the linear hook: one graph, same numbers."""
+    from vllm_fp8_w8a16_sm70_b200 import Fp8LinearMethod
+    x, w, s, bh = make_dense(6, 384, 256, seed=21)
+    layer = types.SimpleNamespace(weight=w.cuda(), weight_scale_inv=s.cuda().to(torch.float16), weight_block_size=[128, 128],
+                                  input_size_per_partition=256, output_size_per_partition=384)
+    method = Fp8LinearMethod((128, 128))
+
+    def fn(t):
+        return method.apply(layer, t) + 1
+
+    eager = fn(x.cuda())
+    torch._dynamo.reset()
+    try:
+        compiled = torch.compile(fn, backend="aot_eager", fullgraph=True)
+        got = compiled(x.cuda())
+    finally:
+        torch._dynamo.reset()
+    assert torch.equal(eager, got)

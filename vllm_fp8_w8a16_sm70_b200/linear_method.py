@@ -39,7 +39,8 @@ def _check_scale_range(s16: torch.Tensor, what: str) -> None:
 
 
 def _apply_2d(layer, x: torch.Tensor, bias, N: int, K: int, scale: torch.Tensor, block_h: int) -> torch.Tensor:
-    observability.on_apply(layer)
+    if not torch.compiler.is_compiling():
+        observability.on_apply(layer)
     orig_shape = x.shape
     x2d = x.reshape(-1, K)
     if x2d.dtype != torch.float16:
@@ -54,7 +55,12 @@ def _apply_2d(layer, x: torch.Tensor, bias, N: int, K: int, scale: torch.Tensor,
         out = ops.w8a16_linear_allreduce(comm, x2d, layer.weight, scale, N, K, block_h, 128)
         layer.w8a16_reduced = True      # tells the caller that this result is already summed over the ranks
     else:
-        out = ops.w8a16_linear(x2d, layer.weight, scale, N, K, block_h, 128)
+        from . import custom_ops
+        if custom_ops.compiling():     # a compiler is tracing: go through the registered op so the graph does not break
+            w8 = layer.weight if layer.weight.dtype == torch.uint8 else layer.weight.view(torch.uint8)
+            out = custom_ops.linear(x2d, w8, scale, N, K, block_h, 128)
+        else:
+            out = ops.w8a16_linear(x2d, layer.weight, scale, N, K, block_h, 128)
         if comm is not None:
             layer.w8a16_reduced = False
     out = out.reshape(orig_shape[:-1] + (N,))

@@ -84,10 +84,15 @@ class Fp8MoEMethod:
         emap = getattr(layer, "expert_map", None)
         if emap is not None and (emap.dtype != torch.int32 or emap.device != x.device):
             emap = emap.to(device=x.device, dtype=torch.int32)
-        out = ops.moe_forward(
-            x_work, tw.contiguous(), ids.contiguous(), layer.w13_weight, getattr(layer, f"w13_{self.weight_scale_name}"),
-            layer.w2_weight, getattr(layer, f"w2_{self.weight_scale_name}"), block_h=self.block_h, expert_map=emap,
-            weight_on_input=bool(getattr(layer, "apply_router_weight_on_input", False)), activation=act)
+        s13, s2 = getattr(layer, f"w13_{self.weight_scale_name}"), getattr(layer, f"w2_{self.weight_scale_name}")
+        on_input = bool(getattr(layer, "apply_router_weight_on_input", False))
+        from . import custom_ops
+        if custom_ops.compiling():     # a compiler is tracing: go through the registered op so the graph does not break
+            out = custom_ops.moe_forward(x_work, tw.contiguous(), ids.contiguous(), layer.w13_weight.view(torch.uint8), s13,
+                                         layer.w2_weight.view(torch.uint8), s2, self.block_h, on_input, act, emap)
+        else:
+            out = ops.moe_forward(x_work, tw.contiguous(), ids.contiguous(), layer.w13_weight, s13, layer.w2_weight, s2,
+                                  block_h=self.block_h, expert_map=emap, weight_on_input=on_input, activation=act)
         return out if out.dtype == x.dtype else out.to(x.dtype)
 
 
