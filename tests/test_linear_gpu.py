@@ -108,10 +108,10 @@ def test_tp_shards_through_engine(ops):
     olin.check_linear(acc, x, full, 2048)
 
 
-@pytest.mark.parametrize("name,N,K", [("qkv", 7168, 5120), ("o_proj", 5120, 5120), ("down", 5120, 25600)])
-@pytest.mark.parametrize("M", [1, 16, 64])
+@pytest.mark.parametrize("name,N,K", [("qkv", 7168, 5120), ("o_proj", 5120, 5120), ("down", 5120, 25600), ("gate_up", 51200, 5120)])
+@pytest.mark.parametrize("M", [1, 16, 64, 2048])
 def test_full_size_decode_shapes_on_device(ops, name, N, K, M):
-    """Full decode-sweep shapes: compared on the device against the bit-exact dequant kernel followed by an
+    """Full decode-sweep shapes (and one prefill batch): compared on the device against the bit-exact dequant kernel followed by an
     fp32 matmul (the reference's own test method, tests/test_phase5_matmul.py:88-175), plus linearity."""
     g = torch.Generator(device="cuda").manual_seed(1)
     w = (torch.randn(N, K, generator=g, device="cuda") * 0.02)
@@ -121,7 +121,7 @@ def test_full_size_decode_shapes_on_device(ops, name, N, K, M):
     del w, blocks
     x = torch.randn(M, K, generator=g, device="cuda").to(torch.float16)
     wdq = ops.fp8_e4m3_to_fp16_block_scaled(q, s, N, K)
-    ref = x.float() @ wdq.float().T
+    ref = torch.cat([x.float() @ wdq[n0:n0 + 8192].float().T for n0 in range(0, N, 8192)], 1)   # bounded fp32 copies
     del wdq
     y = ops.w8a16_linear(x, q, s, N, K)
     olin.check_linear(y.cpu(), x.cpu(), ref.cpu(), K)
