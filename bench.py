@@ -523,6 +523,7 @@ def main() -> None:
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only", default=None, metavar="LAYER:M", help="profiling aid: run one dense case only, e.g. gate_up:16 "
                     "(implies --no-extras --no-cpu-baseline, skips the end-to-end leg)")
+    ap.add_argument("--moe-m", default=None, metavar="M[,M...]", help="--workload moe: tokens per GPU to run (default 1,8,64,256)")
     ap.add_argument("--allreduce", default="fused", choices=["fused", "nccl"],
                     help="N > 1: row-parallel all-reduce fused into the GEMM kernel over peer memory (default) or NCCL after it")
     ap.add_argument("--eager", action="store_true", help="time eager launches instead of CUDA-graph replays (1 GPU)")
@@ -549,7 +550,7 @@ def main() -> None:
     elif args.workload == "prefill":
         out = run_dense(args, world, rank, local, PREFILL_M if world == 1 else PREFILL_M, "prefill")
     else:
-        moe = run_moe(args, world, rank, local)
+        moe = run_moe(args, world, rank, local, tuple(int(m) for m in args.moe_m.split(",")) if args.moe_m else (1, 8, 64, 256))
         best = max(moe["results"], key=lambda r: r["tok_per_s"])
         out = {"metric": "moe_decode_layer_tok_per_s", "value": best["tok_per_s"], "unit": "tok/s", "n_gpus": world, "steps": args.steps,
                "warmup": args.warmup, "ms_per_step": best["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

@@ -224,6 +224,8 @@ __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, ui
 __device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
 
 // Thread-block cluster helpers (synchronous split-K): every thread of every CTA of the cluster arrives and waits.
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
@@ -570,6 +572,25 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         }
     }
 
+    // Likewise the scales of the first segment's first two K blocks (model constants): fetched by the converting warps
+    // before the dependency wait, so that their L2 / HBM latency is not the first thing on the critical path after it.
+    __half pre_cur[C::kWT], pre_nx1[C::kWT];
+    bool pre_ok = false;
+    if (!grouped && warp >= 2 && warp <= 9 && u_begin < u_end) {
+        Seg sg0;
+        get_seg<BT>(p, u_begin, u_end, total_kb, n_tt, units_per_cta, sg0);
+        const int kb_last0 = sg0.kb0 + sg0.nkb - 1;
+#pragma unroll
+        for (int wt = 0; wt < C::kWT; ++wt) {
+            int n = sg0.slab * 128 + (warp & 3) * 32 + lane + wt * p.pair_offset;
+            n = min(n, p.w_rows_per_expert - 1);
+            const int64_t srow0 = (int64_t)(n / p.block_h) * p.Kb;
+            pre_cur[wt] = load_scale_h(p.scales, srow0 + ((sg0.kb0 * BK) >> 7), p.scale_dtype);
+            pre_nx1[wt] = load_scale_h(p.scales, srow0 + ((min(sg0.kb0 + 1, kb_last0) * BK) >> 7), p.scale_dtype);
+        }
+        pre_ok = true;
+    }
+
     // Everything above read only launch parameters and model weights, so under programmatic dependent
     // launch it may have overlapped the tail of the previous kernel in the stream.  From here on that
     // kernel's results (activations, route tables, workspace) are needed.
@@ -854,8 +875,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             __half s_cur[C::kWT], s_nx1[C::kWT];
 #pragma unroll
             for (int wt = 0; wt < C::kWT; ++wt) {
-                s_cur[wt] = load_scale_h(p.scales, srow[wt] + ((sg.kb0 * BK) >> 7), p.scale_dtype);
-                s_nx1[wt] = load_scale_h(p.scales, srow[wt] + ((min(sg.kb0 + 1, kb_last) * BK) >> 7), p.scale_dtype);
+                if (si == 0 && pre_ok) {   // fetched before the dependency wait
+                    s_cur[wt] = pre_cur[wt];
+                    s_nx1[wt] = pre_nx1[wt];
+                } else {
+                    s_cur[wt] = load_scale_h(p.scales, srow[wt] + ((sg.kb0 * BK) >> 7), p.scale_dtype);
+                    s_nx1[wt] = load_scale_h(p.scales, srow[wt] + ((min(sg.kb0 + 1, kb_last) * BK) >> 7), p.scale_dtype);
+                }
             }
             for (int j = 0; j < sg.nkb && ok; ++j) {
                 const int s = rr.stage, sa = ra.stage;
@@ -941,19 +967,23 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 const int chunk = (BT * 32 + S - 1) / S;             // 16-byte groups of the tile reduced by each rank
                 const int lo = (int)rnk * chunk, hi = min(BT * 32, lo + chunk);
                 const uint32_t local_part = s_raw;
+                // all ranks' slices are requested at once (one distributed-shared-memory round trip), then added in
+                // ascending rank = ascending K order: deterministic
                 for (int idx4 = lo + td; idx4 < hi; idx4 += kDequantThreads) {
                     const int ml = idx4 >> 5, nl = (idx4 & 31) * 4;
                     if (ml >= last_sg.rows_valid || n0 + nl >= p.N) continue;
                     float4 g = make_float4(0.f, 0.f, 0.f, 0.f), uu = make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll 4
-                    for (int t = 0; t < S; ++t) {                        // ascending rank = ascending K: deterministic
-                        const uint32_t peer = cluster_map(local_part, (uint32_t)t);
-                        const float4 a = ld_cluster_f4(peer + (uint32_t)idx4 * 16u);
-                        g.x += a.x; g.y += a.y; g.z += a.z; g.w += a.w;
-                        if (PAIRED) {
-                            const float4 b = ld_cluster_f4(peer + (uint32_t)(BT * 32 + idx4) * 16u);
-                            uu.x += b.x; uu.y += b.y; uu.z += b.z; uu.w += b.w;
-                        }
+#pragma unroll
+                    for (int wt = 0; wt < C::kWT; ++wt) {
+                        float4 a[8];
+#pragma unroll
+                        for (int t = 0; t < 8; ++t)
+                            if (t < S) a[t] = ld_cluster_f4(cluster_map(local_part, (uint32_t)t) + (uint32_t)(wt * BT * 32 + idx4) * 16u);
+                        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                        for (int t = 0; t < 8; ++t)
+                            if (t < S) { acc.x += a[t].x; acc.y += a[t].y; acc.z += a[t].z; acc.w += a[t].w; }
+                        if (wt == 0) g = acc; else uu = acc;
                     }
                     const int row = last_sg.row_begin + ml, n = n0 + nl;
                     store_out<PAIRED>(p, out_ptr, row, n, g.x, uu.x);
@@ -963,7 +993,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 }
             }
             if (td == 0) TC_TRACE(0, 200, 5);
-            cluster_sync_all();   // nobody leaves (and frees its shared memory) while a peer may still read it
+            // this CTA has read what it needs from its peers; nobody may leave (and free its shared memory) before
+            // every peer has said the same - the matching wait is taken in the teardown
+            cluster_arrive();
             if (td == 0) TC_TRACE(0, 201, 0);
             if (AR) {
                 Seg last_sg;
@@ -980,9 +1012,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #ifdef W8A16_TC_TRACE
     if (threadIdx.x == 64 && blockIdx.x < 512) g_tc_cta[blockIdx.x][2] = globaltimer_ns_raw();
 #endif
-    if (p.cluster_size > 1 && !(has_work && warp >= 2 && warp <= 9)) {
-        cluster_sync_all();   // the dequant warps of a working CTA take these two inside their branch
-        cluster_sync_all();
+    if (p.cluster_size > 1) {
+        if (!(has_work && warp >= 2 && warp <= 9)) {
+            cluster_sync_all();   // the dequant warps of a working CTA take the first barrier and the second arrive in their branch
+            cluster_arrive();
+        }
+        cluster_wait();
     }
     // ---- teardown: every thread arrives here, also after a timed-out wait ----
     if (*s_dead) {
@@ -1180,7 +1215,15 @@ int max_active_clusters_for(int bt, bool paired, int cs) {
 
 }  // namespace
 
-int tc_block_k(int bt, bool paired) { return (!paired && bt <= 64) ? 128 : 64; }
+int tc_block_k(int bt, bool paired) {
+    static int prefill_bk = -1;   // experiment knob: FP8W8A16_PREFILL_BK=128 uses 128-element K blocks for the 256-token tile
+    if (prefill_bk < 0) {
+        const char* e = getenv("FP8W8A16_PREFILL_BK");
+        prefill_bk = (e && atoi(e) == 128) ? 128 : 64;
+    }
+    if (!paired && bt == 256) return prefill_bk;
+    return (!paired && bt <= 64) ? 128 : 64;
+}
 
 int tc_ctas_per_sm(int bt, bool paired) { return (bt * (paired ? 2 : 1) <= 64) ? 2 : 1; }
 
@@ -1247,7 +1290,9 @@ int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st) {
             case 32: W8A16_TC_CASE(32, 128, false);
             case 64: W8A16_TC_CASE(64, 128, false);
             case 128: W8A16_TC_CASE(128, 64, false);
-            case 256: W8A16_TC_CASE(256, 64, false);
+            case 256:
+                if (tc_block_k(256, false) == 128) W8A16_TC_CASE(256, 128, false);
+                W8A16_TC_CASE(256, 64, false);
         }
     } else {
         switch (bt) {
