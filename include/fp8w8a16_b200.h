@@ -149,6 +149,19 @@ int fp8w8a16_linear_allreduce(fp8w8a16_comm* comm, const uint16_t* x, const uint
 int fp8w8a16_moe_topk_softmax(const void* logits, int logits_dtype, int M, int E, int topk, int renormalize,
                               int32_t* topk_ids, float* topk_weights, void* stream);
 
+/* Router gate and selection in one kernel: logits[m,e] = sum_h x[m,h] * gate_weight[e,h] in fp32 (x FP16 [M,H],
+ * gate_weight [E,H] in FP8W8A16_DTYPE_F16 / _BF16 / _F32, as the model keeps its unquantised router), followed by the
+ * selection of fp8w8a16_moe_topk_softmax on those logits.  The step before the reference's MoE apply: vLLM runs the
+ * gate Linear and fused_topk, the hook only receives their result (vllm_serve.py:2175, 2799-2812).  The routed
+ * weights are multiplied by routed_scale (1 = leave them).  shared_expert_id >= 0 appends one fixed route per token,
+ * (shared_expert_id, weight 1), so that a shared expert stored as one more row of the expert stack is computed by the
+ * same grouped GEMMs and "routed + shared" (vllm_serve.py:2832-2846) costs no extra pass; the output rows then hold
+ * topk + 1 entries.  logits (fp32 [M,E]) may be null.  One CTA per token: meant for decode batches; E <= 512, H a
+ * multiple of 8. */
+int fp8w8a16_moe_router_topk(const uint16_t* x, const void* gate_weight, int gate_dtype, int M, int E, int H, int topk,
+                             int renormalize, int shared_expert_id, float routed_scale, int32_t* topk_ids,
+                             float* topk_weights, float* logits, void* stream);
+
 /* Route table, built on the device without host synchronisation.  topk_ids: R routed slots, int32
  * or int64 (ids_are_i64).  expert_map: optional int32 [n_global_experts] global -> local id, -1 =
  * not on this rank (vllm_serve.py:2237-2243); ids < 0 or unmapped are dropped (they contribute

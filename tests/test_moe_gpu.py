@@ -145,3 +145,54 @@ def test_pieces_gather_grouped_combine(ops):
     want = torch.zeros(M, H)
     want.index_add_(0, sr // topk, y.cpu().float())
     assert torch.allclose(out.cpu().float(), want, atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.parametrize("M,E,H,topk,dtype", [(1, 128, 2048, 8, torch.float16), (7, 128, 2048, 8, torch.bfloat16), (64, 60, 512, 4, torch.float32),
+                                              (3, 8, 64, 8, torch.float16), (33, 256, 1024, 6, torch.bfloat16)])
+def test_router_gemv_topk_fused(ops, M, E, H, topk, dtype):
+    """Gate GEMV + selection in one kernel.  The logits must match an fp32 matmul of the same tensors; given the
+    kernel's own logits the picks must be EXACTLY the oracle's (indices bit-exact, ties to the lowest index)."""
+    g = torch.Generator().manual_seed(M * 1000 + E)
+    x = torch.randn(M, H, generator=g).to(torch.float16)
+    gw = (torch.randn(E, H, generator=g) / H ** 0.5).to(dtype)
+    if M >= 3:
+        gw[5] = gw[2]                       # two experts with identical logits: the lower index must win
+    w, ids, logits = ops.moe_router_topk(x.cuda(), gw.cuda(), topk, True, return_logits=True)
+    ref_logits = x.float() @ gw.float().T
+    assert torch.allclose(logits.cpu(), ref_logits, atol=2e-4, rtol=1e-4)
+    ids_o, w_o = omoe.route_topk(logits.cpu(), topk, True)
+    assert torch.equal(ids.cpu(), ids_o), "routing indices must be bit-exact given the logits"
+    assert torch.allclose(w.cpu(), w_o, atol=1e-6, rtol=1e-5)
+    # same picks as the two-step path (logits -> moe_topk_softmax)
+    w2, ids2 = ops.moe_topk_softmax(logits, topk, True)
+    assert torch.equal(ids2, ids) and torch.equal(w2, w)
+    # fixed shared-expert route and routed scaling
+    ws, idss = ops.moe_router_topk(x.cuda(), gw.cuda(), topk, True, shared_expert_id=E, routed_scale=2.5)
+    assert tuple(idss.shape) == (M, topk + 1) and torch.equal(idss[:, :topk], ids) and bool((idss[:, topk] == E).all())
+    assert torch.allclose(ws[:, :topk], w * 2.5, rtol=1e-6) and bool((ws[:, topk] == 1.0).all())
+
+
+@pytest.mark.parametrize("M", [1, 5, 40])
+def test_moe_block_with_shared_expert(ops, M):
+    """router -> experts -> routed + shared in one pipeline vs the oracle: routed reference + a dense shared MLP."""
+    from vllm_fp8_w8a16_sm70_b200.moe_block import MoEBlock
+    E, I, H, topk = 16, 256, 512, 4
+    d = make_moe(E + 1, I, H, M, topk, seed=77)             # expert E plays the shared expert
+    g = torch.Generator().manual_seed(5)
+    gate = (torch.randn(E, H, generator=g) / H ** 0.5).to(torch.float16)
+    blk = MoEBlock(gate.cuda(), d["w13"][:E].cuda(), d["s13"][:E].cuda(), d["w2"][:E].cuda(), d["s2"][:E].cuda(), topk,
+                   shared=(d["w13"][E].cuda(), d["s13"][E].cuda(), d["w2"][E].cuda(), d["s2"][E].cuda()), routed_scaling_factor=1.5)
+    x = d["x"]
+    out = blk(x.cuda())
+    tw, ids = blk.route(x.cuda())
+    ids_c, tw_c = ids.cpu(), tw.cpu()
+    assert bool((ids_c[:, topk] == E).all())
+    ref = omoe.moe_reference_fp32(x, tw_c, ids_c, d["w13"], d["s13"], d["w2"], d["s2"])      # E + 1 experts, fixed route included
+    omoe.check_moe(out.cpu(), ref)
+    # the shared part alone equals a dense MLP on every token
+    routed_only = omoe.moe_reference_fp32(x, tw_c[:, :topk], ids_c[:, :topk], d["w13"], d["s13"], d["w2"], d["s2"])
+    shared_only = omoe.moe_reference_fp32(x, torch.ones(M, 1), torch.full((M, 1), E), d["w13"], d["s13"], d["w2"], d["s2"])
+    assert torch.allclose(ref, routed_only + shared_only, atol=1e-4, rtol=1e-4)
+    with pytest.raises(ValueError):
+        MoEBlock(gate.cuda(), d["w13"][:E].cuda(), d["s13"][:E].cuda(), d["w2"][:E].cuda(), d["s2"][:E].cuda(), topk,
+                 shared=(d["w13"][E][:256].cuda(), d["s13"][E].cuda(), d["w2"][E].cuda(), d["s2"][E].cuda()))

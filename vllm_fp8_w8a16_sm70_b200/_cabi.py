@@ -45,6 +45,8 @@ PROTOTYPES = {
     "fp8w8a16_linear_allreduce": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                           c_int, c_void_p, c_size_t, c_void_p]),
     "fp8w8a16_moe_topk_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "fp8w8a16_moe_router_topk": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, ctypes.c_float,
+                                         c_void_p, c_void_p, c_void_p, c_void_p]),
     "fp8w8a16_moe_align": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
                                    c_void_p, c_void_p, c_void_p]),
     "fp8w8a16_moe_token_tile": (c_int, [c_int, c_int]),

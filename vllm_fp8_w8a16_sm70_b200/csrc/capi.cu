@@ -58,6 +58,8 @@ int launch_gemv(const __half* x, const uint8_t* w, const void* scales, int scale
                 int block_h, int block_w, void* workspace, size_t workspace_bytes, cudaStream_t st);
 int launch_topk_softmax(const void* logits, int logits_dtype, int M, int E, int topk, int renorm, int* ids, float* weights,
                         cudaStream_t st);
+int launch_router_topk(const __half* x, const void* gate, int gate_dtype, int M, int E, int H, int topk, int renorm, int shared_id,
+                       float routed_scale, int* ids, float* weights, float* logits_out, cudaStream_t st);
 int launch_align(const void* ids, int ids_are_i64, int R, const int* expert_map, int n_global, int E, int bt, int* counts,
                  int* offsets, int* tile_offsets, int* sorted_route, int* inv_pos, cudaStream_t st);
 int launch_gather(const __half* x, const int* sorted_route, const float* topk_w, int R, int topk, int H, int weight_on_input,
@@ -367,6 +369,16 @@ int fp8w8a16_moe_topk_softmax(const void* logits, int logits_dtype, int M, int E
     W8A16_REQUIRE(M >= 0, FP8W8A16_ERR_INVALID, "moe_topk_softmax: negative M");
     W8A16_REQUIRE(M == 0 || (logits && topk_ids && topk_weights), FP8W8A16_ERR_INVALID, "moe_topk_softmax: null pointer");
     return launch_topk_softmax(logits, logits_dtype, M, E, topk, renormalize, topk_ids, topk_weights, (cudaStream_t)stream);
+}
+
+int fp8w8a16_moe_router_topk(const uint16_t* x, const void* gate_weight, int gate_dtype, int M, int E, int H, int topk,
+                             int renormalize, int shared_expert_id, float routed_scale, int32_t* topk_ids, float* topk_weights,
+                             float* logits, void* stream) {
+    W8A16_REQUIRE(M >= 0, FP8W8A16_ERR_INVALID, "moe_router_topk: negative M");
+    W8A16_REQUIRE(M == 0 || (x && gate_weight && topk_ids && topk_weights), FP8W8A16_ERR_INVALID, "moe_router_topk: null pointer");
+    W8A16_REQUIRE(M == 0 || (aligned16(x) && aligned16(gate_weight)), FP8W8A16_ERR_INVALID, "moe_router_topk: x and gate_weight must be 16-byte aligned");
+    return launch_router_topk(reinterpret_cast<const __half*>(x), gate_weight, gate_dtype, M, E, H, topk, renormalize,
+                              shared_expert_id, routed_scale, topk_ids, topk_weights, logits, (cudaStream_t)stream);
 }
 
 int fp8w8a16_moe_token_tile(int R, int num_local_experts) {

@@ -28,14 +28,10 @@ template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; 
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 
+// Top-k softmax of one row of logits by one warp: fp32 softmax, k picks in descending order of logit, ties to the
+// lowest expert index, weights = the picks' probabilities (optionally renormalised to sum to one).
 template <typename T, int PER_LANE>
-__global__ void __launch_bounds__(128) k_topk_softmax(const T* __restrict__ logits, int M, int E, int topk, int renorm,
-                                                      int* __restrict__ ids, float* __restrict__ weights) {
-    pdl_trigger();
-    pdl_wait();
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-    if (warp >= M) return;
-    const T* row = logits + (int64_t)warp * E;
+__device__ __forceinline__ void topk_row(const T* row, int E, int topk, int renorm, int* ids, float* weights, int lane) {
     float v[PER_LANE];
     float mx = -INFINITY;
 #pragma unroll
@@ -85,14 +81,82 @@ __global__ void __launch_bounds__(128) k_topk_softmax(const T* __restrict__ logi
         if ((t & 31) == 31 || t == topk - 1) {  // flush up to 32 picks
             const int t0 = t & ~31;
             if (t0 + lane <= t) {
-                ids[(int64_t)warp * topk + t0 + lane] = isel;
-                weights[(int64_t)warp * topk + t0 + lane] = wsel;
+                ids[t0 + lane] = isel;
+                weights[t0 + lane] = wsel;
             }
         }
     }
     if (renorm) {
         __syncwarp();
-        for (int t = lane; t < topk; t += 32) weights[(int64_t)warp * topk + t] /= wtot;
+        for (int t = lane; t < topk; t += 32) weights[t] /= wtot;
+    }
+}
+
+template <typename T, int PER_LANE>
+__global__ void __launch_bounds__(128) k_topk_softmax(const T* __restrict__ logits, int M, int E, int topk, int renorm,
+                                                      int* __restrict__ ids, float* __restrict__ weights) {
+    pdl_trigger();
+    pdl_wait();
+    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (warp >= M) return;
+    topk_row<T, PER_LANE>(logits + (int64_t)warp * E, E, topk, renorm, ids + (int64_t)warp * topk, weights + (int64_t)warp * topk, lane);
+}
+
+// Router: gate GEMV + top-k softmax in one kernel, one CTA per token.  logit[e] = sum_h x[h] * Wg[e, h] in fp32 (x FP16,
+// gate weight FP16 / BF16 / fp32 as the model keeps it), then the same selection code as k_topk_softmax on the fp32 logits.
+template <typename W, int PER_LANE>
+__global__ void __launch_bounds__(256) k_router_topk(const __half* __restrict__ x, const W* __restrict__ gate, int M, int E, int H,
+                                                     int topk, int renorm, int shared_id, float routed_scale,
+                                                     int* __restrict__ ids, float* __restrict__ weights,
+                                                     float* __restrict__ logits_out) {
+    extern __shared__ __align__(16) unsigned char smem_router[];
+    __half* sx = reinterpret_cast<__half*>(smem_router);                         // [H]
+    float* sl = reinterpret_cast<float*>(smem_router + (size_t)H * sizeof(__half));  // [E]
+    pdl_trigger();
+    pdl_wait();
+    const int m = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x * 8; i < H; i += 256 * 8)
+        *reinterpret_cast<uint4*>(sx + i) = *reinterpret_cast<const uint4*>(x + (int64_t)m * H + i);
+    __syncthreads();
+    for (int e = warp; e < E; e += 8) {
+        const W* wr = gate + (int64_t)e * H;
+        float acc = 0.f;
+        for (int i = lane * 8; i < H; i += 32 * 8) {
+            float wv[8];
+            if (sizeof(W) == 2) {
+                const uint4 q = *reinterpret_cast<const uint4*>(wr + i);
+                const W* h8 = reinterpret_cast<const W*>(&q);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) wv[j] = to_f32<W>(h8[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) wv[j] = to_f32<W>(wr[i + j]);
+            }
+            const uint4 xq = *reinterpret_cast<const uint4*>(sx + i);
+            const __half* x8 = reinterpret_cast<const __half*>(&xq);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = fmaf(__half2float(x8[j]), wv[j], acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            sl[e] = acc;
+            if (logits_out != nullptr) logits_out[(int64_t)m * E + e] = acc;
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        // row stride of the outputs: the picks, plus one fixed slot when a shared expert rides along as expert `shared_id`
+        const int ld = topk + (shared_id >= 0 ? 1 : 0);
+        int* my_ids = ids + (int64_t)m * ld;
+        float* my_w = weights + (int64_t)m * ld;
+        topk_row<float, PER_LANE>(sl, E, topk, renorm, my_ids, my_w, lane);
+        __syncwarp();
+        if (routed_scale != 1.0f)
+            for (int t = lane; t < topk; t += 32) my_w[t] *= routed_scale;
+        if (shared_id >= 0 && lane == 0) {
+            my_ids[topk] = shared_id;
+            my_w[topk] = 1.0f;
+        }
     }
 }
 
@@ -311,6 +375,37 @@ int launch_topk_softmax(const void* logits, int logits_dtype, int M, int E, int 
         case FP8W8A16_DTYPE_BF16: return launch_topk_t(reinterpret_cast<const __nv_bfloat16*>(logits), M, E, topk, renorm, ids, weights, st);
     }
     return fail(FP8W8A16_ERR_INVALID, "topk_softmax: unknown logits dtype %d", logits_dtype);
+}
+
+namespace {
+template <typename W>
+int launch_router_t(const __half* x, const W* gate, int M, int E, int H, int topk, int renorm, int shared_id, float routed_scale,
+                    int* ids, float* weights, float* logits_out, cudaStream_t st) {
+    const int per_lane = (E + 31) / 32;
+    const size_t smem = (size_t)H * sizeof(__half) + (size_t)E * sizeof(float);
+#define W8A16_ROUTER(PL) launch_pdl(k_router_topk<W, PL>, dim3((unsigned)M), dim3(256), smem, st, x, gate, M, E, H, topk, renorm, shared_id, routed_scale, ids, weights, logits_out)
+    if (per_lane <= 1) W8A16_ROUTER(1);
+    else if (per_lane <= 2) W8A16_ROUTER(2);
+    else if (per_lane <= 4) W8A16_ROUTER(4);
+    else if (per_lane <= 8) W8A16_ROUTER(8);
+    else W8A16_ROUTER(16);
+#undef W8A16_ROUTER
+    return check_launch("moe_router_topk");
+}
+}  // namespace
+
+int launch_router_topk(const __half* x, const void* gate, int gate_dtype, int M, int E, int H, int topk, int renorm, int shared_id,
+                       float routed_scale, int* ids, float* weights, float* logits_out, cudaStream_t st) {
+    W8A16_REQUIRE(E >= 1 && E <= 512, FP8W8A16_ERR_UNSUPPORTED, "moe_router_topk: E=%d out of range [1,512]", E);
+    W8A16_REQUIRE(topk >= 1 && topk <= E, FP8W8A16_ERR_INVALID, "moe_router_topk: topk=%d must be in [1,E=%d]", topk, E);
+    W8A16_REQUIRE(H >= 8 && H % 8 == 0 && H <= 16384, FP8W8A16_ERR_UNSUPPORTED, "moe_router_topk: hidden size %d must be a multiple of 8, at most 16384", H);
+    if (M == 0) return 0;
+    switch (gate_dtype) {
+        case FP8W8A16_DTYPE_F32: return launch_router_t(x, reinterpret_cast<const float*>(gate), M, E, H, topk, renorm, shared_id, routed_scale, ids, weights, logits_out, st);
+        case FP8W8A16_DTYPE_F16: return launch_router_t(x, reinterpret_cast<const __half*>(gate), M, E, H, topk, renorm, shared_id, routed_scale, ids, weights, logits_out, st);
+        case FP8W8A16_DTYPE_BF16: return launch_router_t(x, reinterpret_cast<const __nv_bfloat16*>(gate), M, E, H, topk, renorm, shared_id, routed_scale, ids, weights, logits_out, st);
+    }
+    return fail(FP8W8A16_ERR_INVALID, "moe_router_topk: unknown gate weight dtype %d", gate_dtype);
 }
 
 int launch_align(const void* ids, int ids_are_i64, int R, const int* expert_map, int n_global, int E, int bt, int* counts,

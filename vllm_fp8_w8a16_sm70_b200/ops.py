@@ -296,6 +296,32 @@ def moe_topk_softmax(logits: torch.Tensor, topk: int, renormalize: bool = True) 
     return wts, ids
 
 
+def moe_router_topk(x: torch.Tensor, gate_weight: torch.Tensor, topk: int, renormalize: bool = True,
+                    return_logits: bool = False, shared_expert_id: int = -1, routed_scale: float = 1.0):
+    """Router gate GEMV + top-k softmax in one kernel: x float16 [M, H], gate_weight [E, H] (fp16 / bf16 / fp32) ->
+    (weights fp32 [M, topk], ids int32 [M, topk]) and, on request, the fp32 logits [M, E].  Stands in for the gate Linear
+    and ``fused_topk`` that run before the reference's MoE hook (src/fp8_w8a16_sm70/vllm_serve.py:2799-2812).
+    ``shared_expert_id >= 0`` appends the fixed route (that id, weight 1) to every token (outputs are [M, topk + 1]);
+    ``routed_scale`` multiplies the routed weights."""
+    dev = _require_cuda(x, gate_weight)
+    if x.dtype != torch.float16 or x.dim() != 2:
+        raise RuntimeError("x must be float16 [M, H]")
+    if gate_weight.dtype not in _LOGIT_DTYPES or gate_weight.dim() != 2 or gate_weight.shape[1] != x.shape[1]:
+        raise RuntimeError(f"gate_weight must be [E, {x.shape[1]}] in fp32 / fp16 / bf16 (got {tuple(gate_weight.shape)} {gate_weight.dtype})")
+    M, H = x.shape
+    E = gate_weight.shape[0]
+    cols = topk + (1 if shared_expert_id >= 0 else 0)
+    ids = torch.empty((M, cols), dtype=torch.int32, device=dev)
+    w = torch.empty((M, cols), dtype=torch.float32, device=dev)
+    logits = torch.empty((M, E), dtype=torch.float32, device=dev) if return_logits else None
+    with _dev_guard(dev):
+        _cabi.check(_cabi.load().fp8w8a16_moe_router_topk(x.contiguous().data_ptr(), gate_weight.contiguous().data_ptr(),
+                                                           _LOGIT_DTYPES[gate_weight.dtype], M, E, H, topk, 1 if renormalize else 0,
+                                                           int(shared_expert_id), float(routed_scale), ids.data_ptr(), w.data_ptr(), logits.data_ptr() if return_logits else None,
+                                                           _stream(dev)), "fp8w8a16_moe_router_topk")
+    return (w, ids, logits) if return_logits else (w, ids)
+
+
 def moe_token_tile(R: int, num_local_experts: int) -> int:
     return int(_cabi.load().fp8w8a16_moe_token_tile(R, num_local_experts))
 
