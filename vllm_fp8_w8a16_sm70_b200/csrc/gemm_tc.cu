@@ -281,11 +281,14 @@ struct TcCfg {
     // K blocks of the NEXT segment that are converted before the previous segment's epilogue runs
     static constexpr int kDefer = kAccBufs == 2 ? kNA : 0;
     static constexpr int kTmemCols = kUsedCols <= 32 ? 32 : kUsedCols <= 64 ? 64 : kUsedCols <= 128 ? 128 : kUsedCols <= 256 ? 256 : 512;
-    static constexpr int kBudget = (kCtasPerSm == 2 ? 112 : 225) * 1024 - 2048;  // dynamic shared memory we allow ourselves
+    // grouped mode keeps the route table's two offset arrays (up to 256 experts + 1 each) in shared memory
+    static constexpr int kTabExperts = 256;
+    static constexpr int kTabBytes = 2 * (kTabExperts + 1) * 4 + 8;
+    static constexpr int kBudget = (kCtasPerSm == 2 ? 112 : 225) * 1024 - 2048 - kTabBytes;  // dynamic shared memory we allow ourselves
     static constexpr int kNSraw = kBudget / (kRawBytes + kXBytes);
     static constexpr int kNS = kNSraw > 8 ? 8 : kNSraw;        // TMA ring stages
     static constexpr int kNumBars = 4 * kNS + 2 * kNA + 2;
-    static constexpr int kSmemBytes = 1024 + kNS * (kRawBytes + kXBytes) + kNumBars * 8 + 64;
+    static constexpr int kSmemBytes = 1024 + kNS * (kRawBytes + kXBytes) + kNumBars * 8 + 64 + kTabBytes;
     static_assert(kNS >= 2, "not enough shared memory for a 2-stage TMA ring");
     static_assert(kNA >= 2, "not enough TMEM for two dequantised stages");
     static_assert(kTmemCols * kCtasPerSm <= 512, "co-resident CTAs exceed TMEM");
@@ -342,7 +345,8 @@ struct Seg {
 };
 
 template <int BT>
-__device__ __forceinline__ void get_seg(const TcParams& p, int u, int u_end, int total_kb, int n_tt, int units_per_cta, Seg& s) {
+__device__ __forceinline__ void get_seg(const TcParams& p, const int* tile_off, const int* exp_off, int u, int u_end, int total_kb,
+                                        int n_tt, int units_per_cta, Seg& s) {
     const int v = u / total_kb;
     s.kb0 = u - v * total_kb;
     s.nkb = min(total_kb - s.kb0, u_end - u);
@@ -362,11 +366,11 @@ __device__ __forceinline__ void get_seg(const TcParams& p, int u, int u_end, int
         int lo = 0, hi = p.num_experts;  // largest e with tile_offsets[e] <= tt
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
-            if (p.tile_offsets[mid] <= tt) lo = mid; else hi = mid;
+            if (tile_off[mid] <= tt) lo = mid; else hi = mid;
         }
         s.expert = lo;
-        s.row_begin = p.expert_offsets[lo] + (tt - p.tile_offsets[lo]) * BT;
-        s.rows_valid = min(BT, p.expert_offsets[lo + 1] - s.row_begin);
+        s.row_begin = exp_off[lo] + (tt - tile_off[lo]) * BT;
+        s.rows_valid = min(BT, exp_off[lo + 1] - s.row_begin);
     } else {
         s.row_begin = tt * BT;
         s.rows_valid = min(BT, p.M - s.row_begin);
@@ -491,6 +495,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(gen_tail);
     volatile int* s_dead = reinterpret_cast<volatile int*>(gen_tail + 4);
     volatile int* s_ticket = reinterpret_cast<volatile int*>(gen_tail + 8);
+    int* s_tab = reinterpret_cast<int*>(gen_tail + 64);   // [kTabExperts + 1] tile offsets, then [kTabExperts + 1] row offsets
+    const int* tab_tile = p.tile_offsets;                 // route-table offsets: global, or their shared-memory copy
+    const int* tab_exp = p.expert_offsets;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -560,7 +567,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     if (!grouped && warp == 0 && lane == 0) {
         for (int u = u_begin; u < u_end && w_preissued < kNS;) {
             Seg sg;
-            get_seg<BT>(p, u, u_end, total_kb, n_tt, units_per_cta, sg);
+            get_seg<BT>(p, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
             const int w_row = sg.slab * 128;
             for (int j = 0; j < sg.nkb && w_preissued < kNS; ++j, ++w_preissued) {
                 const int s = w_preissued;  // ring is empty: stage index == unit index, no wait needed
@@ -578,7 +585,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     bool pre_ok = false;
     if (!grouped && warp >= 2 && warp <= 9 && u_begin < u_end) {
         Seg sg0;
-        get_seg<BT>(p, u_begin, u_end, total_kb, n_tt, units_per_cta, sg0);
+        get_seg<BT>(p, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, sg0);
         const int kb_last0 = sg0.kb0 + sg0.nkb - 1;
 #pragma unroll
         for (int wt = 0; wt < C::kWT; ++wt) {
@@ -599,7 +606,17 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     if (threadIdx.x == 0 && blockIdx.x < 512) g_tc_cta[blockIdx.x][1] = globaltimer_ns_raw();
 #endif
     if (grouped) {
-        n_tt = p.tile_offsets[p.num_experts];
+        if (p.num_experts <= C::kTabExperts) {
+            // every segment start searches these tables: keep them on chip
+            for (int i = threadIdx.x; i <= p.num_experts; i += kThreadsTc) {
+                s_tab[i] = p.tile_offsets[i];
+                s_tab[C::kTabExperts + 1 + i] = p.expert_offsets[i];
+            }
+            __syncthreads();
+            tab_tile = s_tab;
+            tab_exp = s_tab + C::kTabExperts + 1;
+        }
+        n_tt = tab_tile[p.num_experts];
         set_range();
     }
     const bool has_work = u_begin < u_end;  // uniform for the whole CTA
@@ -622,7 +639,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             int it = 0;   // K blocks handled so far; the first w_preissued of them already have their weight tile in flight
             for (int u = u_begin; u < u_end && ok;) {
                 Seg sg;
-                get_seg<BT>(p, u, u_end, total_kb, n_tt, units_per_cta, sg);
+                get_seg<BT>(p, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
                 const int w_row = sg.expert * p.w_rows_per_expert + sg.slab * 128;
                 for (int j = 0; j < sg.nkb; ++j, ++it) {
                     const int s = ring.stage;
@@ -858,7 +875,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         int stop = 0;
         for (int u = u_begin; u < u_end; ++si) {
             Seg sg;
-            get_seg<BT>(p, u, u_end, total_kb, n_tt, units_per_cta, sg);
+            get_seg<BT>(p, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
             u += sg.nkb;
             const int n0 = sg.slab * 128;
             // scale-grid rows for this thread's weight row(s); clamped so tail rows stay in bounds
@@ -875,13 +892,30 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             __half s_cur[C::kWT], s_nx1[C::kWT];
 #pragma unroll
             for (int wt = 0; wt < C::kWT; ++wt) {
-                if (si == 0 && pre_ok) {   // fetched before the dependency wait
+                if (pre_ok) {   // fetched before the dependency wait (first segment) or during the previous segment
                     s_cur[wt] = pre_cur[wt];
                     s_nx1[wt] = pre_nx1[wt];
                 } else {
                     s_cur[wt] = load_scale_h(p.scales, srow[wt] + ((sg.kb0 * BK) >> 7), p.scale_dtype);
                     s_nx1[wt] = load_scale_h(p.scales, srow[wt] + ((min(sg.kb0 + 1, kb_last) * BK) >> 7), p.scale_dtype);
                 }
+            }
+            pre_ok = false;
+            if (u < u_end) {
+                // the first scales of the NEXT segment travel while this one is converted: with short segments (a few
+                // K blocks per tile, as in the MoE down projection) their latency would otherwise open every tile
+                Seg nx;
+                get_seg<BT>(p, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, nx);
+                const int kb_last_n = nx.kb0 + nx.nkb - 1;
+#pragma unroll
+                for (int wt = 0; wt < C::kWT; ++wt) {
+                    int n = nx.slab * 128 + r + wt * p.pair_offset;
+                    n = min(n, p.w_rows_per_expert - 1);
+                    const int64_t srow_n = (int64_t)nx.expert * p.scale_expert_stride + (int64_t)(n / p.block_h) * p.Kb;
+                    pre_cur[wt] = load_scale_h(p.scales, srow_n + ((nx.kb0 * BK) >> 7), p.scale_dtype);
+                    pre_nx1[wt] = load_scale_h(p.scales, srow_n + ((min(nx.kb0 + 1, kb_last_n) * BK) >> 7), p.scale_dtype);
+                }
+                pre_ok = true;
             }
             for (int j = 0; j < sg.nkb && ok; ++j) {
                 const int s = rr.stage, sa = ra.stage;
@@ -959,7 +993,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (td == 0) TC_TRACE(0, 200, 4);
             if (!stop) {
                 Seg last_sg;   // the one segment of this CTA
-                get_seg<BT>(p, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
+                get_seg<BT>(p, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
                 const int S = p.cluster_size;
                 uint32_t rnk;
                 asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rnk));
@@ -999,7 +1033,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (td == 0) TC_TRACE(0, 201, 0);
             if (AR) {
                 Seg last_sg;
-                get_seg<BT>(p, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
+                get_seg<BT>(p, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
                 uint32_t rnk;
                 asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rnk));
                 const int chunk = (BT * 32 + p.cluster_size - 1) / p.cluster_size;
