@@ -107,6 +107,7 @@ def test_observability_summary_without_gpu(lib, monkeypatch, capsys):
     obs.reset()
     monkeypatch.setenv("FP8W8A16_VARIANT_LOG_EVERY", "2")
     monkeypatch.setenv("FP8W8A16_PREFIX_PROFILE", "1")
+    obs.reload_env()
     import types
     obs.on_apply(types.SimpleNamespace(prefix="model.layers.0.mlp.down_proj"))
     assert capsys.readouterr().err == ""
@@ -114,6 +115,7 @@ def test_observability_summary_without_gpu(lib, monkeypatch, capsys):
     err = capsys.readouterr().err
     assert "kernel variant counts after 2 hook calls" in err and "model.layers.0.mlp.down_proj: calls=2" in err
     monkeypatch.setenv("FP8W8A16_VARIANT_LOG_EVERY", "0")
+    obs.reload_env()
     obs.on_apply(None)
     assert capsys.readouterr().err == ""
     obs.reset()

@@ -19,7 +19,7 @@ from typing import Optional
 
 import torch
 
-from . import observability, ops
+from . import custom_ops, observability, ops
 from .backend import select_backend
 
 
@@ -39,13 +39,17 @@ def _check_scale_range(s16: torch.Tensor, what: str) -> None:
 
 
 def _apply_2d(layer, x: torch.Tensor, bias, N: int, K: int, scale: torch.Tensor, block_h: int) -> torch.Tensor:
-    if not torch.compiler.is_compiling():
+    compiling = torch.compiler.is_compiling()
+    if not compiling:
         observability.on_apply(layer)
     orig_shape = x.shape
-    x2d = x.reshape(-1, K)
+    x2d = x if x.dim() == 2 else x.reshape(-1, K)
     if x2d.dtype != torch.float16:
         x2d = x2d.to(torch.float16)
-    x2d = x2d.contiguous()
+    if not x2d.is_contiguous():
+        x2d = x2d.contiguous()
+    if x2d.shape[-1] != K:
+        raise RuntimeError(f"x must be [..., {K}] (got {tuple(x.shape)})")
     # A row-parallel layer that carries a peer-memory communicator (``layer.w8a16_peer_comm``, set by the integrator
     # together with ``reduce_results = False``) gets its tensor-parallel all-reduce done inside the GEMM kernel; a
     # bias would have to be added on one rank only before the reduce (vllm_serve.py:2937-2945), so such calls and
@@ -55,15 +59,25 @@ def _apply_2d(layer, x: torch.Tensor, bias, N: int, K: int, scale: torch.Tensor,
         out = ops.w8a16_linear_allreduce(comm, x2d, layer.weight, scale, N, K, block_h, 128)
         layer.w8a16_reduced = True      # tells the caller that this result is already summed over the ranks
     else:
-        from . import custom_ops
-        if custom_ops.compiling():     # a compiler is tracing: go through the registered op so the graph does not break
+        if compiling:                   # a compiler is tracing: go through the registered op so the graph does not break
             w8 = layer.weight if layer.weight.dtype == torch.uint8 else layer.weight.view(torch.uint8)
             out = custom_ops.linear(x2d, w8, scale, N, K, block_h, 128)
         else:
-            out = ops.w8a16_linear(x2d, layer.weight, scale, N, K, block_h, 128)
+            if not x2d.is_cuda:
+                raise RuntimeError(f"x is on {x.device}: the engine runs on CUDA tensors only (there is no CPU path)")
+            # per-layer plan: pointers, shapes and the C entry point resolved once (rebuilt if the tensors were replaced)
+            plan = getattr(layer, "_w8a16_plan", None)
+            if plan is None or not plan.matches(layer.weight, scale) or x2d.device != plan.dev:
+                plan = ops.LinearPlan(layer.weight, scale, N, K, block_h)
+                try:
+                    layer._w8a16_plan = plan
+                except AttributeError:
+                    pass
+            out = plan.run(x2d)
         if comm is not None:
             layer.w8a16_reduced = False
-    out = out.reshape(orig_shape[:-1] + (N,))
+    if len(orig_shape) != 2:
+        out = out.reshape(orig_shape[:-1] + (N,))
     if bias is not None:
         out = out + bias.to(out.dtype)
     if out.dtype != x.dtype:

@@ -36,6 +36,17 @@ def _env_int(name: str, default: int = 0) -> int:
         return default
 
 
+# the hooks call on_apply() on every forward: the environment is read once (reload_env() re-reads it)
+_every: Optional[int] = None
+_prefix_profile = False
+
+
+def reload_env() -> None:
+    global _every, _prefix_profile
+    _every = _env_int("FP8W8A16_VARIANT_LOG_EVERY")
+    _prefix_profile = _env_int("FP8W8A16_PREFIX_PROFILE") != 0
+
+
 def selfcheck_enabled() -> bool:
     return _env_int("FP8W8A16_SELFCHECK") != 0
 
@@ -69,11 +80,13 @@ def selfcheck_linear(weight: torch.Tensor, scale: torch.Tensor, N: int, K: int, 
 def on_apply(layer=None) -> None:
     """Count one hook call; print the summary every FP8W8A16_VARIANT_LOG_EVERY calls."""
     global _calls
-    every = _env_int("FP8W8A16_VARIANT_LOG_EVERY")
-    if every <= 0:
+    if _every is None:
+        reload_env()
+    if _every <= 0:
         return
+    every = _every
     _calls += 1
-    if _env_int("FP8W8A16_PREFIX_PROFILE"):
+    if _prefix_profile:
         _prefix_calls[getattr(layer, "prefix", "<?>")] += 1
     if _calls % every == 0:
         rank = torch.distributed.get_rank() if torch.distributed.is_available() and torch.distributed.is_initialized() else 0
