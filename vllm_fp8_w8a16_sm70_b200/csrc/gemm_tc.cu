@@ -345,8 +345,8 @@ struct Seg {
 };
 
 template <int BT>
-__device__ __forceinline__ void get_seg(const TcParams& p, const int* tile_off, const int* exp_off, int u, int u_end, int total_kb,
-                                        int n_tt, int units_per_cta, Seg& s) {
+__device__ __forceinline__ void get_seg(const TcParams& p, bool grouped, const int* tile_off, const int* exp_off, int u, int u_end,
+                                        int total_kb, int n_tt, int units_per_cta, Seg& s) {
     const int v = u / total_kb;
     s.kb0 = u - v * total_kb;
     s.nkb = min(total_kb - s.kb0, u_end - u);
@@ -362,7 +362,7 @@ __device__ __forceinline__ void get_seg(const TcParams& p, const int* tile_off, 
     s.slab = s.tile / n_tt;             // token tiles fastest: concurrently running CTAs share a weight slab
     const int tt = s.tile - s.slab * n_tt;
     s.expert = 0;
-    if (p.expert_offsets != nullptr) {
+    if (grouped) {
         int lo = 0, hi = p.num_experts;  // largest e with tile_offsets[e] <= tt
         while (hi - lo > 1) {
             const int mid = (lo + hi) >> 1;
@@ -529,7 +529,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     // ---- this CTA's unit range ----
     // Dense problems know it from the launch parameters alone; grouped ones read the tile count from
     // the route table, which the previous kernel wrote, so they must wait for it first.
-    const bool grouped = p.expert_offsets != nullptr;
+    const bool grouped = !AR && p.expert_offsets != nullptr;   // the fused all-reduce build is dense only
     const int total_kb = (p.K + BK - 1) / BK;
     const int n_slabs = (p.N + 127) / 128;
     const int cta = blockIdx.x;
@@ -567,7 +567,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     if (!grouped && warp == 0 && lane == 0) {
         for (int u = u_begin; u < u_end && w_preissued < kNS;) {
             Seg sg;
-            get_seg<BT>(p, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
+            get_seg<BT>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
             const int w_row = sg.slab * 128;
             for (int j = 0; j < sg.nkb && w_preissued < kNS; ++j, ++w_preissued) {
                 const int s = w_preissued;  // ring is empty: stage index == unit index, no wait needed
@@ -585,7 +585,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     bool pre_ok = false;
     if (!grouped && warp >= 2 && warp <= 9 && u_begin < u_end) {
         Seg sg0;
-        get_seg<BT>(p, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, sg0);
+        get_seg<BT>(p, grouped, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, sg0);
         const int kb_last0 = sg0.kb0 + sg0.nkb - 1;
 #pragma unroll
         for (int wt = 0; wt < C::kWT; ++wt) {
@@ -639,7 +639,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             int it = 0;   // K blocks handled so far; the first w_preissued of them already have their weight tile in flight
             for (int u = u_begin; u < u_end && ok;) {
                 Seg sg;
-                get_seg<BT>(p, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
+                get_seg<BT>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
                 const int w_row = sg.expert * p.w_rows_per_expert + sg.slab * 128;
                 for (int j = 0; j < sg.nkb; ++j, ++it) {
                     const int s = ring.stage;
@@ -875,7 +875,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         int stop = 0;
         for (int u = u_begin; u < u_end; ++si) {
             Seg sg;
-            get_seg<BT>(p, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
+            get_seg<BT>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
             u += sg.nkb;
             const int n0 = sg.slab * 128;
             // scale-grid rows for this thread's weight row(s); clamped so tail rows stay in bounds
@@ -901,11 +901,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 }
             }
             pre_ok = false;
-            if (u < u_end) {
+            if (!AR && u < u_end) {   // (not in the fused all-reduce build: it has no registers to spare and few segments per CTA)
                 // the first scales of the NEXT segment travel while this one is converted: with short segments (a few
                 // K blocks per tile, as in the MoE down projection) their latency would otherwise open every tile
                 Seg nx;
-                get_seg<BT>(p, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, nx);
+                get_seg<BT>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, nx);
                 const int kb_last_n = nx.kb0 + nx.nkb - 1;
 #pragma unroll
                 for (int wt = 0; wt < C::kWT; ++wt) {
@@ -993,7 +993,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (td == 0) TC_TRACE(0, 200, 4);
             if (!stop) {
                 Seg last_sg;   // the one segment of this CTA
-                get_seg<BT>(p, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
+                get_seg<BT>(p, grouped, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
                 const int S = p.cluster_size;
                 uint32_t rnk;
                 asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rnk));
@@ -1009,14 +1009,18 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     float4 g = make_float4(0.f, 0.f, 0.f, 0.f), uu = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
                     for (int wt = 0; wt < C::kWT; ++wt) {
-                        float4 a[8];
-#pragma unroll
-                        for (int t = 0; t < 8; ++t)
-                            if (t < S) a[t] = ld_cluster_f4(cluster_map(local_part, (uint32_t)t) + (uint32_t)(wt * BT * 32 + idx4) * 16u);
+                        constexpr int kBatch = AR ? 4 : 8;   // the fused all-reduce build has fewer registers to spare
                         float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
-                        for (int t = 0; t < 8; ++t)
-                            if (t < S) { acc.x += a[t].x; acc.y += a[t].y; acc.z += a[t].z; acc.w += a[t].w; }
+                        for (int t0 = 0; t0 < 8; t0 += kBatch) {
+                            float4 a[kBatch];
+#pragma unroll
+                            for (int t = 0; t < kBatch; ++t)
+                                if (t0 + t < S) a[t] = ld_cluster_f4(cluster_map(local_part, (uint32_t)(t0 + t)) + (uint32_t)(wt * BT * 32 + idx4) * 16u);
+#pragma unroll
+                            for (int t = 0; t < kBatch; ++t)
+                                if (t0 + t < S) { acc.x += a[t].x; acc.y += a[t].y; acc.z += a[t].z; acc.w += a[t].w; }
+                        }
                         if (wt == 0) g = acc; else uu = acc;
                     }
                     const int row = last_sg.row_begin + ml, n = n0 + nl;
@@ -1033,7 +1037,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (td == 0) TC_TRACE(0, 201, 0);
             if (AR) {
                 Seg last_sg;
-                get_seg<BT>(p, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
+                get_seg<BT>(p, grouped, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
                 uint32_t rnk;
                 asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rnk));
                 const int chunk = (BT * 32 + p.cluster_size - 1) / p.cluster_size;
