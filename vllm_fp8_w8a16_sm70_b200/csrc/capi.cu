@@ -205,7 +205,12 @@ int grouped_gemm(const __half* x_sorted, const uint8_t* w, const void* scales, i
     L.p.row_weight = row_weight;
     L.p.activation = paired;
     L.p.n_token_tiles = 0;
-    L.p.no_split = tiles_ub > (int64_t)tc_max_tiles_with_tickets() ? 1 : 0;
+    // Whole tiles instead of stream-K when a tile is only a few K blocks long and there are at least two per CTA (the MoE
+    // down projection: K = I): splitting such a tile over two CTAs costs a partial-tile round trip and a ticket per tile,
+    // more than the last-wave imbalance of at most one short tile.
+    const int total_kb = (K + bk - 1) / bk;
+    const bool short_tiles = total_kb <= 8 && tiles_ub >= 2ll * tc_grid(bt, paired != 0);
+    L.p.no_split = (tiles_ub > (int64_t)tc_max_tiles_with_tickets() || short_tiles) ? 1 : 0;
     L.p.tickets = reinterpret_cast<unsigned int*>(workspace);
     L.p.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kTicketBytes);
     L.w = w;

@@ -293,7 +293,15 @@ k_gather(const __half* __restrict__ x, const int* __restrict__ sorted_route, con
     const float wt = topk_w[route];
     const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)(route / topk) * H);
     if (!weight_on_input) {
-        for (int i = lane; i < vecs; i += 32) dst[i] = __ldg(src + i);
+        int i = lane;
+        for (; i + 96 < vecs; i += 128) {   // four 16-byte loads in flight per lane
+            const uint4 a = __ldg(src + i), b = __ldg(src + i + 32), c = __ldg(src + i + 64), d = __ldg(src + i + 96);
+            dst[i] = a;
+            dst[i + 32] = b;
+            dst[i + 64] = c;
+            dst[i + 96] = d;
+        }
+        for (; i < vecs; i += 32) dst[i] = __ldg(src + i);
         if (lane == 0) w_sorted[pos] = wt;
     } else {
         // reference: route_x * route_w.unsqueeze(-1) on FP16 tensors (vllm_serve.py:1868-1870)
@@ -327,16 +335,24 @@ k_combine(const __half* __restrict__ y_sorted, const int* __restrict__ inv_pos, 
         float acc[8];
 #pragma unroll
         for (int c = 0; c < 8; ++c) acc[c] = 0.f;
-        for (int j = 0; j < topk; ++j) {
-            const int pos = s_pos[j];
-            if (pos < 0) continue;
-            const uint4 v = __ldg(reinterpret_cast<const uint4*>(y_sorted + (int64_t)pos * H) + i);
-            const __half2* h = reinterpret_cast<const __half2*>(&v);
+        // eight routes' rows are requested together (one L2 round trip per batch instead of one per route); the sum
+        // still runs in route order
+        for (int j0 = 0; j0 < topk; j0 += 8) {
+            uint4 v[8];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                const float2 f = __half22float2(h[c]);
-                acc[2 * c] += f.x;
-                acc[2 * c + 1] += f.y;
+            for (int t = 0; t < 8; ++t) {
+                const int pos = (j0 + t < topk) ? s_pos[j0 + t] : -1;
+                v[t] = pos >= 0 ? __ldg(reinterpret_cast<const uint4*>(y_sorted + (int64_t)pos * H) + i) : make_uint4(0u, 0u, 0u, 0u);
+            }
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+                const __half2* h = reinterpret_cast<const __half2*>(&v[t]);   // +0 for a dropped route: exact
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    const float2 f = __half22float2(h[c]);
+                    acc[2 * c] += f.x;
+                    acc[2 * c + 1] += f.y;
+                }
             }
         }
         uint4 o;
