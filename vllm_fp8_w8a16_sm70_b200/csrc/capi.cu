@@ -167,6 +167,13 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
 }
 
 int token_tile_for(int R, int E) {
+    static int forced = -1;   // FP8W8A16_MOE_BT=16|32|64|128 overrides the choice (tuning aid)
+    if (forced < 0) {
+        const char* e = getenv("FP8W8A16_MOE_BT");
+        const int v = e ? atoi(e) : 0;
+        forced = (v == 16 || v == 32 || v == 64 || v == 128) ? v : 0;
+    }
+    if (forced) return forced;
     const int avg = (R + E - 1) / E;
     int bt = tc_pick_bt(2 * avg);
     if (bt > 128) bt = 128;  // the paired gate/up kernel keeps two accumulators in TMEM: 128 tokens at most

@@ -148,6 +148,8 @@ class ExpertParallelMoE:
         self.local_experts = num_experts // self.ep_size
         assert num_experts % self.ep_size == 0 and w13.shape[0] == self.local_experts
         self._experts = expert_fn or self._engine_experts
+        import os
+        self.coalesce = os.environ.get("FP8W8A16_EP_COALESCE", "0") == "1"
 
     def _engine_experts(self, rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
         ones = torch.ones(rows.shape[0], 1, dtype=torch.float32, device=rows.device)
@@ -174,19 +176,29 @@ class ExpertParallelMoE:
         P = self.ep_size
         M, H = x.shape
         topk = topk_ids.shape[-1]
-        # one collective instead of three: activations, expert ids and route weights of a token travel as one
-        # packed row of bytes (decode-sized exchanges are latency-bound, not bandwidth-bound)
         ids32 = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
-        row_bytes = 2 * H + 8 * topk
-        packed = torch.empty((M, row_bytes), dtype=torch.uint8, device=x.device)
-        packed[:, :2 * H] = x.contiguous().view(torch.uint8).reshape(M, 2 * H)
-        packed[:, 2 * H:2 * H + 4 * topk] = ids32.contiguous().view(torch.uint8).reshape(M, 4 * topk)
-        packed[:, 2 * H + 4 * topk:] = topk_weights.contiguous().view(torch.uint8).reshape(M, 4 * topk)
-        gathered = torch.empty((P * M, row_bytes), dtype=torch.uint8, device=x.device)
-        dist.all_gather_into_tensor(gathered, packed, group=self.group)
-        xg = gathered[:, :2 * H].contiguous().view(torch.float16).reshape(P * M, H)
-        ig = gathered[:, 2 * H:2 * H + 4 * topk].contiguous().view(torch.int32).reshape(P * M, topk)
-        wg = gathered[:, 2 * H + 4 * topk:].contiguous().view(torch.float32).reshape(P * M, topk)
+        if self.coalesce and x.is_cuda and dist.get_backend(self.group) == "nccl":
+            # opt-in (FP8W8A16_EP_COALESCE=1): activations, expert ids and route weights gathered by ONE grouped NCCL
+            # launch straight into the three tensors the layer takes, without the packing and unpacking kernels
+            xg = x.new_empty((P * M, H))
+            ig = ids32.new_empty((P * M, topk))
+            wg = topk_weights.new_empty((P * M, topk))
+            with dist._coalescing_manager(group=self.group, device=x.device):
+                dist.all_gather_into_tensor(xg, x.contiguous(), group=self.group)
+                dist.all_gather_into_tensor(ig, ids32.contiguous(), group=self.group)
+                dist.all_gather_into_tensor(wg, topk_weights.contiguous(), group=self.group)
+        else:
+            # other backends: one collective of packed rows (activations, ids, weights of a token as bytes)
+            row_bytes = 2 * H + 8 * topk
+            packed = torch.empty((M, row_bytes), dtype=torch.uint8, device=x.device)
+            packed[:, :2 * H] = x.contiguous().view(torch.uint8).reshape(M, 2 * H)
+            packed[:, 2 * H:2 * H + 4 * topk] = ids32.contiguous().view(torch.uint8).reshape(M, 4 * topk)
+            packed[:, 2 * H + 4 * topk:] = topk_weights.contiguous().view(torch.uint8).reshape(M, 4 * topk)
+            gathered = torch.empty((P * M, row_bytes), dtype=torch.uint8, device=x.device)
+            dist.all_gather_into_tensor(gathered, packed, group=self.group)
+            xg = gathered[:, :2 * H].contiguous().view(torch.float16).reshape(P * M, H)
+            ig = gathered[:, 2 * H:2 * H + 4 * topk].contiguous().view(torch.int32).reshape(P * M, topk)
+            wg = gathered[:, 2 * H + 4 * topk:].contiguous().view(torch.float32).reshape(P * M, topk)
         if getattr(self, "_emap", None) is None or self._emap.device != x.device:
             rank = dist.get_rank(self.group)
             emap = torch.full((self.num_experts,), -1, dtype=torch.int32)
