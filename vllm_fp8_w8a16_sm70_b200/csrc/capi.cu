@@ -152,6 +152,21 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
     W8A16_REQUIRE(L.max_units < (1ll << 31), FP8W8A16_ERR_UNSUPPORTED, "linear: problem too large for 32-bit work indices");
     L.p.cluster_size = tc_cluster_size(tiles, (K + bk - 1) / bk, bt, false);
     L.cluster_tiles = tiles;
+    // Optional (FP8W8A16_HYBRID_STREAMK=1): stream-K with at least one tile per CTA (gate_up at decode sizes: 400 tiles on
+    // 296 CTAs) lets every CTA take whole tiles first, stored directly, and splits only the remainder.  Measured on B200
+    // it is a wash (gate_up +1 % at 2-8 tokens, -1..3 % at 32-64), so the plain even split stays the default.
+    static int hybrid = -1;
+    if (hybrid < 0) {
+        const char* e = getenv("FP8W8A16_HYBRID_STREAMK");
+        hybrid = (e && atoi(e) == 1) ? 1 : 0;
+    }
+    const int64_t grid = tc_grid(bt, false);
+    if (hybrid && ar == nullptr && !L.p.no_split && L.p.cluster_size <= 1 && tiles >= grid) {
+        if (tiles % grid == 0)
+            L.p.no_split = 1;                     // the tiles divide evenly: nothing to split at all
+        else
+            L.p.whole_rounds = (int)(tiles / grid);
+    }
     if (ar != nullptr && ar->world > 1) {
         W8A16_REQUIRE(N % 4 == 0, FP8W8A16_ERR_UNSUPPORTED, "linear_allreduce: N must be a multiple of 4 (got %d)", N);
         W8A16_REQUIRE((int64_t)M * N <= ar->part_elems, FP8W8A16_ERR_UNSUPPORTED,

@@ -342,22 +342,35 @@ __device__ __forceinline__ void store_out(const TcParams& p, __half* out, int ro
 struct Seg {
     int tile, slab, expert, row_begin, rows_valid, kb0, nkb;
     int first_c, n_contrib;
+    int tkey;   // the tile's index in the space the stream-K split is computed in (== tile unless whole tiles come first)
 };
 
-template <int BT>
+template <int BT, bool HYBRID = true>
 __device__ __forceinline__ void get_seg(const TcParams& p, bool grouped, const int* tile_off, const int* exp_off, int u, int u_end,
                                         int total_kb, int n_tt, int units_per_cta, Seg& s) {
     const int v = u / total_kb;
     s.kb0 = u - v * total_kb;
     s.nkb = min(total_kb - s.kb0, u_end - u);
+    const int rounds = HYBRID ? p.whole_rounds : 0;   // (compiled out of the paired and the fused all-reduce builds)
     if (p.no_split) {
         // whole tiles, dealt round-robin: at any moment the CTAs work on gridDim.x consecutive tiles (token tiles
         // fastest), so a weight slab is in flight for all its token tiles at once and is read from HBM once
         const int per_cta = units_per_cta / total_kb;
         const int c = v / per_cta;
         s.tile = (v - c * per_cta) * (int)gridDim.x + c;
+        s.tkey = s.tile;
+    } else if (rounds > 0) {
+        // hybrid: the CTA's own coordinate space is [0, rounds) whole tiles, then its share of the remaining tiles
+        if (v < rounds) {
+            s.tile = (int)blockIdx.x + v * (int)gridDim.x;
+            s.tkey = -1;
+        } else {
+            s.tkey = v - rounds;
+            s.tile = rounds * (int)gridDim.x + s.tkey;
+        }
     } else {
         s.tile = v;
+        s.tkey = v;
     }
     s.slab = s.tile / n_tt;             // token tiles fastest: concurrently running CTAs share a weight slab
     const int tt = s.tile - s.slab * n_tt;
@@ -375,12 +388,12 @@ __device__ __forceinline__ void get_seg(const TcParams& p, bool grouped, const i
         s.row_begin = tt * BT;
         s.rows_valid = min(BT, p.M - s.row_begin);
     }
-    if (p.no_split) {
+    if (p.no_split || s.tkey < 0) {
         s.first_c = 0;
         s.n_contrib = 1;
     } else {
-        s.first_c = (s.tile * total_kb) / units_per_cta;
-        s.n_contrib = ((s.tile + 1) * total_kb - 1) / units_per_cta - s.first_c + 1;
+        s.first_c = (s.tkey * total_kb) / units_per_cta;
+        s.n_contrib = ((s.tkey + 1) * total_kb - 1) / units_per_cta - s.first_c + 1;
     }
 }
 
@@ -472,6 +485,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     static_assert(!(AR && PAIRED), "the fused all-reduce is a dense (row-parallel) mode");
     using C = TcCfg<BT, BK, PAIRED>;
     constexpr int kNS = C::kNS, kNA = C::kNA;
+    constexpr bool kHybrid = !PAIRED && !AR;   // whole tiles before the stream-K share: dense launches only
 
     // Programmatic dependent launch: let the next kernel of the stream start its own set-up as soon as
     // this grid's CTAs are resident; it will wait (griddepcontrol.wait) for this grid to finish before
@@ -534,6 +548,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     const int n_slabs = (p.N + 127) / 128;
     const int cta = blockIdx.x;
     int n_tt = p.n_token_tiles, total_units = 0, units_per_cta = 0, u_begin = 0, u_end = 0;
+    int jump_from = -1, jump_to = 0;
     auto set_range = [&]() {
         const int total_tiles = n_tt * n_slabs;
         total_units = total_tiles * total_kb;
@@ -552,11 +567,27 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             const int mine = cta < total_tiles ? (total_tiles - cta + (int)gridDim.x - 1) / (int)gridDim.x : 0;
             u_begin = cta * units_per_cta;
             u_end = u_begin + mine * total_kb;
+        } else if (kHybrid && p.whole_rounds > 0) {
+            // hybrid: whole tiles first (coordinates [0, lenA)), then this CTA's stream-K share [bB, eB) of the remaining
+            // tiles, placed at lenA + [bB, eB) so that tile boundaries stay at multiples of total_kb
+            const int lenA = p.whole_rounds * total_kb;
+            const int units_b = (total_tiles - p.whole_rounds * (int)gridDim.x) * total_kb;
+            units_per_cta = (units_b + (int)gridDim.x - 1) / (int)gridDim.x;
+            const int bB = min(units_b, cta * units_per_cta), eB = min(units_b, bB + units_per_cta);
+            u_begin = 0;
+            u_end = lenA + eB;
+            jump_from = lenA;
+            jump_to = lenA + bB;
         } else {
             units_per_cta = (total_units + (int)gridDim.x - 1) / (int)gridDim.x;
             u_begin = cta * units_per_cta;
             u_end = min(total_units, u_begin + units_per_cta);
         }
+    };
+    // next coordinate after a segment of nkb blocks (the hybrid schedule skips from the whole tiles to the CTA's share)
+    auto advance = [&](int u, int nkb) -> int {
+        u += nkb;
+        return u == jump_from ? jump_to : u;
     };
     if (!grouped) set_range();
 
@@ -567,7 +598,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     if (!grouped && warp == 0 && lane == 0) {
         for (int u = u_begin; u < u_end && w_preissued < kNS;) {
             Seg sg;
-            get_seg<BT>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
+            get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
             const int w_row = sg.slab * 128;
             for (int j = 0; j < sg.nkb && w_preissued < kNS; ++j, ++w_preissued) {
                 const int s = w_preissued;  // ring is empty: stage index == unit index, no wait needed
@@ -575,7 +606,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 tma_load_2d(s_raw + s * C::kRawBytes, &map_w, bar_full_raw + 8 * s, (sg.kb0 + j) * BK, w_row);
                 if (PAIRED) tma_load_2d(s_raw + s * C::kRawBytes + 128 * BK, &map_w, bar_full_raw + 8 * s, (sg.kb0 + j) * BK, w_row + p.pair_offset);
             }
-            u += sg.nkb;
+            u = advance(u, sg.nkb);
         }
     }
 
@@ -585,7 +616,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     bool pre_ok = false;
     if (!grouped && warp >= 2 && warp <= 9 && u_begin < u_end) {
         Seg sg0;
-        get_seg<BT>(p, grouped, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, sg0);
+        get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, sg0);
         const int kb_last0 = sg0.kb0 + sg0.nkb - 1;
 #pragma unroll
         for (int wt = 0; wt < C::kWT; ++wt) {
@@ -639,7 +670,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             int it = 0;   // K blocks handled so far; the first w_preissued of them already have their weight tile in flight
             for (int u = u_begin; u < u_end && ok;) {
                 Seg sg;
-                get_seg<BT>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
+                get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
                 const int w_row = sg.expert * p.w_rows_per_expert + sg.slab * 128;
                 for (int j = 0; j < sg.nkb; ++j, ++it) {
                     const int s = ring.stage;
@@ -660,7 +691,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         tma_load_2d(s_x + s * C::kXBytes + sl * (BT * 128), &map_x, bar_full_x + 8 * s, k0 + sl * 64, sg.row_begin);
                     ring.advance(kNS);
                 }
-                u += sg.nkb;
+                u = advance(u, sg.nkb);
             }
         }
     } else if (warp == 1 || warp == 10) {
@@ -708,7 +739,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     rx.advance(kNS);
                 }
                 if (ok) umma_commit(bar_acc + 8 * (si % C::kAccBufs));  // accumulators of this segment are complete
-                u += nkb;
+                u = advance(u, nkb);
             }
         }
     } else if (warp >= 2 && warp <= 9) {
@@ -769,7 +800,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 const int n = n0 + n_local;
                 // partial tile: a workspace slot (stream-K), or this CTA's idle raw-tile ring (cluster split-K)
                 float* part = clustered ? reinterpret_cast<float*>(smem_dyn + (s_raw - dyn_base))
-                                        : p.partial + (int64_t)partial_slot(cta, sg.tile, total_kb, units_per_cta) * kTileFloats;
+                                        : p.partial + (int64_t)partial_slot(cta, sg.tkey, total_kb, units_per_cta) * kTileFloats;
 #pragma unroll 1
                 for (int c0 = 0; c0 < kColsPerWarp; c0 += 8) {
                     const int col = hk * kColsPerWarp + c0;
@@ -844,7 +875,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         for (int t = 0; t < 8; ++t) {
                             const int cc = sg.first_c + min(c0 + t, sg.n_contrib - 1);   // clamped: extra loads are ignored below
                             const float4* ps = reinterpret_cast<const float4*>(
-                                p.partial + (int64_t)partial_slot(cc, sg.tile, total_kb, units_per_cta) * kTileFloats);
+                                p.partial + (int64_t)partial_slot(cc, sg.tkey, total_kb, units_per_cta) * kTileFloats);
                             a[t] = __ldcg(&ps[idx4]);
                             if (PAIRED) b[t] = __ldcg(&ps[BT * 32 + idx4]);
                         }
@@ -875,8 +906,8 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         int stop = 0;
         for (int u = u_begin; u < u_end; ++si) {
             Seg sg;
-            get_seg<BT>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
-            u += sg.nkb;
+            get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
+            u = advance(u, sg.nkb);
             const int n0 = sg.slab * 128;
             // scale-grid rows for this thread's weight row(s); clamped so tail rows stay in bounds
             int64_t srow[C::kWT];
@@ -905,7 +936,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 // the first scales of the NEXT segment travel while this one is converted: with short segments (a few
                 // K blocks per tile, as in the MoE down projection) their latency would otherwise open every tile
                 Seg nx;
-                get_seg<BT>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, nx);
+                get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, nx);
                 const int kb_last_n = nx.kb0 + nx.nkb - 1;
 #pragma unroll
                 for (int wt = 0; wt < C::kWT; ++wt) {
@@ -993,7 +1024,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (td == 0) TC_TRACE(0, 200, 4);
             if (!stop) {
                 Seg last_sg;   // the one segment of this CTA
-                get_seg<BT>(p, grouped, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
+                get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
                 const int S = p.cluster_size;
                 uint32_t rnk;
                 asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rnk));
@@ -1037,7 +1068,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             if (td == 0) TC_TRACE(0, 201, 0);
             if (AR) {
                 Seg last_sg;
-                get_seg<BT>(p, grouped, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
+                get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
                 uint32_t rnk;
                 asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rnk));
                 const int chunk = (BT * 32 + p.cluster_size - 1) / p.cluster_size;
