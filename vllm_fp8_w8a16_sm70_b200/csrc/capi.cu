@@ -152,13 +152,16 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
     W8A16_REQUIRE(L.max_units < (1ll << 31), FP8W8A16_ERR_UNSUPPORTED, "linear: problem too large for 32-bit work indices");
     L.p.cluster_size = tc_cluster_size(tiles, (K + bk - 1) / bk, bt, false);
     L.cluster_tiles = tiles;
-    // Optional (FP8W8A16_HYBRID_STREAMK=1): stream-K with at least one tile per CTA (gate_up at decode sizes: 400 tiles on
+    // Optional (library built with -DW8A16_HYBRID_STREAMK and FP8W8A16_HYBRID_STREAMK=1): stream-K with at least one tile per CTA (gate_up at decode sizes: 400 tiles on
     // 296 CTAs) lets every CTA take whole tiles first, stored directly, and splits only the remainder.  Measured on B200
     // it is a wash (gate_up +1 % at 2-8 tokens, -1..3 % at 32-64), so the plain even split stays the default.
     static int hybrid = -1;
     if (hybrid < 0) {
         const char* e = getenv("FP8W8A16_HYBRID_STREAMK");
         hybrid = (e && atoi(e) == 1) ? 1 : 0;
+#ifndef W8A16_HYBRID_STREAMK
+        hybrid = 0;
+#endif
     }
     const int64_t grid = tc_grid(bt, false);
     if (hybrid && ar == nullptr && !L.p.no_split && L.p.cluster_size <= 1 && tiles >= grid) {

@@ -485,7 +485,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     static_assert(!(AR && PAIRED), "the fused all-reduce is a dense (row-parallel) mode");
     using C = TcCfg<BT, BK, PAIRED>;
     constexpr int kNS = C::kNS, kNA = C::kNA;
+#ifdef W8A16_HYBRID_STREAMK
     constexpr bool kHybrid = !PAIRED && !AR;   // whole tiles before the stream-K share: dense launches only
+#else
+    constexpr bool kHybrid = false;            // measured neutral on B200: left out of the default build (it costs registers)
+#endif
 
     // Programmatic dependent launch: let the next kernel of the stream start its own set-up as soon as
     // this grid's CTAs are resident; it will wait (griddepcontrol.wait) for this grid to finish before
