@@ -372,23 +372,30 @@ def run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, wo
     ev_comp = [torch.cuda.Event() for _ in groups]
     used = [False] * len(groups)
 
+    # views into the staging buffers are the same every step: build them once
+    x_views = {(g, ci): dev_x[x_off:x_off + M * k_in].view(M, k_in)
+               for g, (M, cases, _, _) in enumerate(groups) for ci, (_, k_in, _, x_off, _) in enumerate(cases)}
+    y_views = {(g, ci): host_y[y_off:y_off + M * n_out].view(M, n_out)
+               for g, (M, cases, _, _) in enumerate(groups) for ci, (_, _, n_out, _, y_off) in enumerate(cases)}
+    copy_in = [(dev_x[x_lo:x_hi], host_x[x_lo:x_hi]) for _, _, x_lo, x_hi in groups]
+
     def step(i):
         lay = layers[i % len(layers)]
         with torch.cuda.stream(s_in):                # this step's activations, group by group
             for g, (M, cases, x_lo, x_hi) in enumerate(groups):
                 if used[g]:
                     s_in.wait_event(ev_comp[g])      # the previous step's GEMMs of this group have read the buffer
-                dev_x[x_lo:x_hi].copy_(host_x[x_lo:x_hi], non_blocking=True)
+                copy_in[g][0].copy_(copy_in[g][1], non_blocking=True)
                 ev_in[g].record(s_in)
         results = []
         for g, (M, cases, x_lo, x_hi) in enumerate(groups):
             cur.wait_event(ev_in[g])
-            for name, k_in, n_out, x_off, y_off in cases:
+            for ci, (name, k_in, n_out, x_off, y_off) in enumerate(cases):
                 layer = lay[name]
-                y = method.apply(layer, dev_x[x_off:x_off + M * k_in].view(M, k_in))
+                y = method.apply(layer, x_views[(g, ci)])
                 if world > 1 and layer.mode == "row" and not layer.w8a16_reduced:
                     dist.all_reduce(y)
-                results.append((y, host_y[y_off:y_off + M * n_out].view(M, n_out)))
+                results.append((y, y_views[(g, ci)]))
             ev_comp[g].record(cur)
             used[g] = True
         with torch.cuda.stream(s_out):               # results leave as their group finishes, under the next GEMMs
