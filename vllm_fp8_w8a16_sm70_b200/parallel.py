@@ -177,10 +177,13 @@ class ExpertParallelMoE:
         M, H = x.shape
         topk = topk_ids.shape[-1]
         ids32 = topk_ids if topk_ids.dtype == torch.int32 else topk_ids.to(torch.int32)
-        if self.coalesce and x.is_cuda and dist.get_backend(self.group) == "nccl":
+        # grouped launch or packed rows: measured, the grouped form wins on 2 GPUs at every batch (60 vs 67 us at 1 token per
+        # GPU, 139 vs 152 us at 64) and on 8 GPUs from ~1000 gathered tokens on (267 vs 285 us at 256 per GPU), while for
+        # small gathers on 8 GPUs three grouped all-gathers cost more than one (94 vs 80 us at 1 token per GPU)
+        grouped_gather = self.coalesce and (P <= 2 or P * M >= 1024)
+        if grouped_gather and x.is_cuda and dist.get_backend(self.group) == "nccl":
             # activations, expert ids and route weights gathered by ONE grouped NCCL launch straight into the three tensors
-            # the layer takes, without packing and unpacking kernels (FP8W8A16_EP_COALESCE=0 selects the packed exchange);
-            # measured on 2 GPUs: 60 vs 67 us per layer at 1 token per GPU, 139 vs 152 us at 64
+            # the layer takes, without packing and unpacking kernels (FP8W8A16_EP_COALESCE=0 always takes the packed exchange)
             xg = x.new_empty((P * M, H))
             ig = ids32.new_empty((P * M, topk))
             wg = topk_weights.new_empty((P * M, topk))
