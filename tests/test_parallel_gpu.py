@@ -126,8 +126,7 @@ def test_tp_and_ep_on_two_gpus(lib):
     _run(2)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 4 or os.environ.get("FP8W8A16_TEST_ALL_GPUS") != "1",
-                    reason="needs four or more GPUs and FP8W8A16_TEST_ALL_GPUS=1 (opt-in: not yet run on a 4- or 8-GPU box)")
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four or more GPUs")
 def test_tp_and_ep_on_all_gpus(lib):
     """The same checks with every GPU of the box as a rank (4 or 8): seven peers' packets per tile in the fused all-reduce."""
     _run(8 if torch.cuda.device_count() >= 8 else 4)
