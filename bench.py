@@ -415,14 +415,14 @@ def run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, wo
         step(i)
     drain()
     # This leg is host-paced (28 Python calls per 0.75 ms of GPU work), so one scheduler hiccup or a garbage collection
-    # inside ten steps moves it by tens of percent: the collector is paused and the median of three passes of K steps
-    # is reported (all three are listed).
+    # inside ten steps moves it by tens of percent: the collector is paused and the median of five passes of K steps
+    # is reported (all five are listed).
     import gc
     passes = []
     gc_was_on = gc.isenabled()
     gc.disable()
     try:
-        for _ in range(3):
+        for _ in range(5):
             barrier_sync(world)
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
@@ -438,7 +438,7 @@ def run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, wo
     ms = statistics.median(passes)
     common = {"ms_per_step": round(ms, 4), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "api": "Fp8LinearMethod.apply",
               "copies": "pinned host buffers, pipelined per token count on two copy streams",
-              "passes_ms_per_step": [round(v, 4) for v in passes], "stat": f"median of 3 passes of {args.steps} steps"}
+              "passes_ms_per_step": [round(v, 4) for v in passes], "stat": f"median of 5 passes of {args.steps} steps"}
     if workload == "decode":
         return {"value": round(bytes_step / ms / 1e6, 2), "unit": "GB/s", **common}
     return {"value": round(flops_step / ms / 1e9, 2), "unit": "TFLOP/s", **common}
