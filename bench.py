@@ -307,7 +307,7 @@ def run_dense(args, world, rank, local, m_list, workload: str) -> dict:
                 "frac_of_nominal_8TBps": round(ach / NOMINAL_HBM_GBS, 4),
                 # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the committed ncu capture of the
                 # gate_up M = 16 case (profiles/k_gemm_tc_decode_gate_up_m16.md); its algorithmic bytes are 263,950,336
-                "traffic": 272.20e6, "traffic_case": "gate_up[51200,5120] M=16, algorithmic 263.95e6 B"}
+                "traffic": 272.86e6, "traffic_case": "gate_up[51200,5120] M=16, algorithmic 263.95e6 B"}
         value, unit, metric = bytes_step / ms_step / 1e6, "GB/s", "w8a16_decode_gemv_hbm_GBps"
     else:
         ach = sum(2 * c["M"] * shape_of(stack, c["layer"])[0] * shape_of(stack, c["layer"])[1] for c in cases) / sum(c["ms"] for c in cases) / 1e9
