@@ -159,3 +159,27 @@ def test_tp_shards_reassemble_the_full_layer():
     assert (sh.N, sh.K) == (128, 176) and tuple(sh.scale.shape) == (128, 2) and sh.block_h == 1
     with pytest.raises(ValueError):
         ck.shard(ck.block_weight(*_quant(128, 1408, 42)), "row", 8, 0)
+
+
+def test_module_construction_follows_the_reference_positional_order(tmp_path):
+    """``FP8W8A16Linear(ext, weight_fp8, weight_scale, block_h, block_w, bias)`` and
+    ``from_safetensors(ext, st_path, weight_key, scale_key)`` exactly as the reference's own test constructs it
+    (reference: tests/test_phase_b_module.py:178, src/fp8_w8a16_sm70/module.py:31-40, 65-76).  No kernel runs."""
+    from vllm_fp8_w8a16_sm70_b200 import FP8W8A16Linear
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(256, 384, generator=g) * 0.02).to(torch.float8_e4m3fn)
+    s = torch.rand(2, 3, generator=g).to(torch.bfloat16)
+    f = tmp_path / "one.safetensors"
+    st.save_file({"l.weight": w, "l.weight_scale_inv": s}, str(f))
+    ext = object()
+    layer = FP8W8A16Linear.from_safetensors(ext, f, "l.weight", "l.weight_scale_inv", device="cpu")
+    assert layer.ext is ext and (layer.N, layer.K, layer.block_h, layer.block_w) == (256, 384, 128, 128)
+    assert layer.weight_fp8.dtype == torch.uint8 and layer.weight_fp8.numel() == 256 * 384
+    assert torch.equal(layer.weight_fp8.reshape(256, 384), w.view(torch.uint8))
+    assert layer.weight_scale.dtype == torch.float16 and torch.equal(layer.weight_scale.reshape(2, 3), s.to(torch.float16))
+    again = FP8W8A16Linear(None, w.view(torch.uint8), s.to(torch.float16), 128, 128, torch.zeros(256))
+    assert again.bias is not None and again.bias.dtype == torch.float16
+    with pytest.raises(AssertionError):
+        FP8W8A16Linear(None, w, s.to(torch.float16))            # float8 tensor where raw bytes are expected
+    with pytest.raises(RuntimeError):
+        layer(torch.zeros(1, 384, dtype=torch.float16))         # CPU input: the engine has no CPU path

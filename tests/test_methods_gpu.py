@@ -61,7 +61,9 @@ def test_module_equals_raw_op(lib):
     # reference: tests/test_phase_b_module.py (module == raw kernel bit-exact; 3-D input)
     from vllm_fp8_w8a16_sm70_b200 import FP8W8A16Linear, ops
     x, w, s, bh = make_dense(6, 256, 384, seed=2)
-    mod = FP8W8A16Linear(w, s.to(torch.float16)).cuda()
+    ext = object()                               # the reference's loaded extension goes first; accepted and unused
+    mod = FP8W8A16Linear(ext, w, s.to(torch.float16)).cuda()
+    assert mod.ext is ext
     y = mod(x.reshape(2, 3, 384).cuda())
     raw = ops.w8a16_linear(x.cuda(), w.cuda(), s.to(torch.float16).cuda(), 256, 384)
     assert tuple(y.shape) == (2, 3, 256) and torch.equal(y.reshape(6, 256).view(torch.int16), raw.view(torch.int16))

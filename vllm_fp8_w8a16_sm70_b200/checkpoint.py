@@ -325,4 +325,4 @@ def to_linear_module(w: Fp8Weight, device="cuda"):
     """A ready :class:`FP8W8A16Linear` on ``device``."""
     from .module import FP8W8A16Linear
     d = w.to(device)
-    return FP8W8A16Linear(d.weight, d.scale, d.block_h, BLOCK, d.bias)
+    return FP8W8A16Linear(None, d.weight, d.scale, d.block_h, BLOCK, d.bias)

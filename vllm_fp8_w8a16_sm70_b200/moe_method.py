@@ -97,17 +97,35 @@ class Fp8MoEMethod:
 
 
 class CompressedTensorsFp8MoEMethod(Fp8MoEMethod):
-    """compressed-tensors FP8 experts with per-output-channel scales ``[E, rows, 1]``.  The
-    reference keeps w13 FP8 with the channel scale expanded to a ``block_h = 1`` grid and stores w2
-    as FP16 because its kernels need K % 128 == 0 (compressed_tensors_v100.py:1090-1106, :931-950);
-    here both stay FP8: the grouped GEMM takes any K that is a multiple of 16 (e.g. I/tp = 176)."""
+    """compressed-tensors FP8 experts (the hooks the reference assigns onto ``CompressedTensorsW8A8Fp8MoEMethod``,
+    compressed_tensors_v100.py:1041-1229).  Scale layouts, as the reference's ``_dequant_expert`` accepts them
+    (:1060-1071): per output channel ``[E, rows, 1]`` / ``[E, rows]``, per tensor ``[E]`` (and, for a fused w13 whose
+    gate and up shards were quantised separately, ``[E, 2]``), or block ``[E, rows/128, K/128]``.  The reference keeps
+    w13 FP8 with the channel scale expanded to a ``block_h = 1`` grid and stores w2 as FP16 because its kernels need
+    K % 128 == 0 (compressed_tensors_v100.py:1090-1106, :931-950); here both stay FP8: the grouped GEMM takes any K
+    that is a multiple of 16 (e.g. I/tp = 176)."""
 
     def __init__(self, weight_quant=None, input_quant=None, moe=None, layer_name=None, strategy: str = "CHANNEL"):
         super().__init__(quant_config=None, weight_block_size=None)
+        strat = getattr(weight_quant, "strategy", None)
+        if strat is not None:
+            strategy = str(getattr(strat, "name", None) or getattr(strat, "value", None) or strat)
         self.strategy = strategy.upper()
         self.block_quant = "BLOCK" in self.strategy
         self.weight_scale_name = "weight_scale"
         self.block_h = 128 if self.block_quant else 1
+
+    @staticmethod
+    def _row_scales(name: str, s: torch.Tensor, E: int, rows: int) -> torch.Tensor:
+        """Any of the non-block layouts -> one FP16 scale per (expert, weight row), ``[E, rows, 1]``."""
+        n = s.numel()
+        if n == E * rows:
+            return s.reshape(E, rows, 1)
+        if n == E:
+            return s.reshape(E, 1, 1).expand(E, rows, 1)
+        if n == 2 * E and name == "w13" and rows % 2 == 0:      # one scale per logical shard: gate rows, then up rows
+            return s.reshape(E, 2, 1).repeat_interleave(rows // 2, dim=1)
+        raise ValueError(f"{name}: cannot map {n} scales ({tuple(s.shape)}) onto [{E},{rows}] weight rows")
 
     def process_weights_after_loading(self, layer) -> None:
         if getattr(layer, "_already_called_process_weights_after_loading", False):
@@ -121,12 +139,14 @@ class CompressedTensorsFp8MoEMethod(Fp8MoEMethod):
             s = getattr(layer, f"{name}_weight_scale")
             s = (s.data if hasattr(s, "data") else s).to(torch.float16)
             if not self.block_quant:
-                if s.numel() != E * rows:
-                    raise ValueError(f"{name}: expected one scale per (expert, row), got {s.numel()} for [{E},{rows}]")
-                s = s.reshape(E, rows, 1).expand(E, rows, -(-K // 128))
+                s = self._row_scales(name, s, E, rows).expand(E, rows, -(-K // 128))
+            elif tuple(s.shape) != (E, -(-rows // 128), -(-K // 128)):
+                raise ValueError(f"{name}: block scale grid {tuple(s.shape)} does not match weight [{E},{rows},{K}]")
             _check_scale_range(s, f"{getattr(layer, 'prefix', 'moe')}.{name}")
             _set(layer, f"{name}_weight_scale", s.contiguous())
             _set(layer, f"{name}_weight", w.contiguous())
+        layer.w13_input_scale = None
+        layer.w2_input_scale = None
         layer._already_called_process_weights_after_loading = True
 
     def get_fused_moe_quant_config(self, layer):

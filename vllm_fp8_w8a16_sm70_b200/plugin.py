@@ -14,6 +14,9 @@ Only the hot-path hooks are replaced:
 * ``Fp8MoEMethod`` / ``Fp8OnlineMoEMethod``: ``process_weights_after_loading``, ``apply`` (5- and 6-argument
   forms), ``maybe_make_prepare_finalize``
 * ``CompressedTensorsW8A16Fp8.process_weights_after_loading`` / ``.apply_weights``
+* ``CompressedTensorsW8A8Fp8MoEMethod.__init__`` / ``.process_weights_after_loading`` / ``.apply`` /
+  ``.get_fused_moe_quant_config`` (the four attributes the reference assigns, compressed_tensors_v100.py:1226-1229);
+  the experts stay FP8-resident here instead of being dequantised to FP16 at load
 """
 
 from __future__ import annotations
@@ -96,7 +99,57 @@ def install() -> List[str]:
 
         patched.append(_patch(VCT, "process_weights_after_loading", ct_pwal))
         patched.append(_patch(VCT, "apply_weights", ct_apply))
+    patched.extend(_install_ct_moe())
     return patched
+
+
+def _ct_moe_class():
+    """The compressed-tensors FP8 MoE method class: a submodule of ``compressed_tensors_moe`` in newer vLLM, defined
+    inline in that module in older ones (the reference binds to whichever exists, compressed_tensors_v100.py:1003-1010)."""
+    try:
+        from vllm.model_executor.layers.quantization.compressed_tensors.compressed_tensors_moe import (
+            compressed_tensors_moe_w8a8_fp8 as mod)
+    except Exception:
+        try:
+            from vllm.model_executor.layers.quantization.compressed_tensors import compressed_tensors_moe as mod
+        except Exception:
+            return None
+    return getattr(mod, "CompressedTensorsW8A8Fp8MoEMethod", None)
+
+
+def _install_ct_moe() -> List[str]:
+    cls = _ct_moe_class()
+    if cls is None:
+        return []
+    orig_init = cls.__init__
+
+    def shim_of(self):
+        shim = getattr(self, "_b200_moe", None)
+        if shim is None:
+            shim = self._b200_moe = _mm.CompressedTensorsFp8MoEMethod(getattr(self, "weight_quant", None))
+        return shim
+
+    def ct_moe_init(self, weight_quant, input_quant, moe, layer_name=None):
+        orig_init(self, weight_quant, input_quant, moe, layer_name)
+        self._b200_moe = _mm.CompressedTensorsFp8MoEMethod(weight_quant, input_quant, moe, layer_name)
+
+    def ct_moe_pwal(self, layer):
+        shim_of(self).process_weights_after_loading(layer)
+
+    def ct_moe_apply(self, layer, x, topk_weights, topk_ids, *shared, **kw):
+        return shim_of(self).apply(layer, x, topk_weights, topk_ids)
+
+    def ct_moe_quant_config(self, layer):
+        return None
+
+    return [_patch(cls, "__init__", ct_moe_init), _patch(cls, "process_weights_after_loading", ct_moe_pwal),
+            _patch(cls, "apply", ct_moe_apply), _patch(cls, "get_fused_moe_quant_config", ct_moe_quant_config)]
+
+
+def register() -> None:
+    """``vllm.general_plugins`` entry point (declared in pyproject.toml): vLLM calls it once per process at start-up.
+    Builds nothing and touches no GPU; a missing library surfaces at the first layer that calls into the engine."""
+    install()
 
 
 def uninstall() -> None:
