@@ -346,7 +346,7 @@ def run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, wo
             lin = stack.lin(name, ci)
             objs[name] = types.SimpleNamespace(weight=lin.w, weight_scale_inv=lin.s, weight_block_size=[128, 128],
                                                input_size_per_partition=lin.K, output_size_per_partition=lin.N, mode=lin.mode,
-                                               w8a16_peer_comm=lin.comm, w8a16_reduced=False)
+                                               w8a16_peer_comm=lin.comm, bias=None)
         layers.append(objs)
     # One pinned HOST buffer holds every activation matrix of a step, one holds every result.  Per step every input is
     # copied host -> device and every result device -> host, pipelined per token count: while the GEMMs of one group run,
@@ -393,8 +393,8 @@ def run_dense_e2e(args, stack, m_list, world, device, bytes_step, flops_step, wo
             for ci, (name, k_in, n_out, x_off, y_off) in enumerate(cases):
                 layer = lay[name]
                 y = method.apply(layer, x_views[(g, ci)])
-                if world > 1 and layer.mode == "row" and not layer.w8a16_reduced:
-                    dist.all_reduce(y)
+                if world > 1 and layer.mode == "row" and layer.w8a16_peer_comm is None:
+                    dist.all_reduce(y)     # (with a communicator attached the hook returns the reduced result on every path)
                 results.append((y, y_views[(g, ci)]))
             ev_comp[g].record(cur)
             used[g] = True

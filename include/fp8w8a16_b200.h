@@ -128,7 +128,15 @@ int fp8w8a16_linear_noalloc(const uint16_t* x, const uint8_t* w, const void* sca
  * max_out_elems bounds M*N of a call (the buffer takes about (10 * world + 2) bytes per element); timeout_ms
  * (0 = 2000) bounds every wait for a peer: when it runs out the kernel gives up, out is not written for the
  * affected tiles and fp8w8a16_device_status reports bit 128.  N must be a multiple of 4.
- * Calls are CUDA-graph capturable (launches are counted on the device). */
+ * Calls are CUDA-graph capturable (launches are counted on the device).
+ *
+ * The launch number lives on each rank's device and advances by one per fused launch; the ranks only agree while
+ * they make the same launches.  After a one-sided launch (one rank raised before launching, or a wait ran out and
+ * status bit 128 was reported) every later fused call would mismatch.  fp8w8a16_comm_reset puts a rank back to
+ * launch number zero with an empty inbox (two device memsets enqueued on `stream`); it is a COLLECTIVE in the host's
+ * hands: every rank must call it, none may have a fused launch in flight on any rank while the memsets run (device
+ * synchronise + host barrier before), and none may launch again before all have finished (synchronise + barrier
+ * after).  The reference has no counterpart: its all-reduce is vLLM's. */
 #define FP8W8A16_COMM_HANDLE_BYTES 64
 typedef struct fp8w8a16_comm fp8w8a16_comm;
 int fp8w8a16_comm_create(int rank, int world, int64_t max_out_elems, unsigned int timeout_ms, fp8w8a16_comm** comm);
@@ -137,6 +145,7 @@ int fp8w8a16_comm_attach(fp8w8a16_comm* comm, int peer, const void* handle);
 int fp8w8a16_comm_attach_ptr(fp8w8a16_comm* comm, int peer, void* peer_base);
 void* fp8w8a16_comm_base(const fp8w8a16_comm* comm);
 size_t fp8w8a16_comm_bytes(const fp8w8a16_comm* comm);
+int fp8w8a16_comm_reset(fp8w8a16_comm* comm, void* stream);
 int fp8w8a16_comm_destroy(fp8w8a16_comm* comm);
 int fp8w8a16_linear_allreduce(fp8w8a16_comm* comm, const uint16_t* x, const uint8_t* w, const void* scales,
                               int scale_dtype, uint16_t* out, int M, int N, int K, int block_h, int block_w,

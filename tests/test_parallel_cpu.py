@@ -78,7 +78,43 @@ def _comm_failure_worker(rank, world, port, q):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("worker", [_tp_worker, _ep_worker, _comm_failure_worker])
+def _hook_path_worker(rank, world, port, q):
+    """The vLLM-facing hook with a communicator attached must (a) pick its path from rank-invariant facts - the bias
+    ARGUMENT arrives on rank 0 only - and (b) return the reduced result on the plain path too.  The GEMM is the oracle's
+    (the engine cannot run on CPU); a fused call would raise here, which is exactly what shows that both ranks avoided it."""
+    import types
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from vllm_fp8_w8a16_sm70_b200 import linear_method as lm, parallel as par
+    x, w, s, bh = make_dense(5, 256, 512, seed=3)
+    wr, sr = par.shard_row_parallel(w, s.to(torch.float16), world, rank)
+    xs = x[:, rank * 256:(rank + 1) * 256].contiguous()
+    lm._plain_2d = lambda layer, x2d, scale, N, K, block_h, compiling: olin.oracle_linear_fp32(x2d, layer.weight, scale, block_h).to(torch.float16)
+    lm.observability.on_apply = lambda layer: None
+    bias = (torch.arange(256, dtype=torch.float32) * 1e-2).to(torch.float16)
+    comm = types.SimpleNamespace(max_out_elems=1 << 20)            # large enough: only the bias keeps the call off the fused path
+    lay = types.SimpleNamespace(weight=wr, weight_scale_inv=sr, weight_block_size=[128, 128], input_size_per_partition=256,
+                                output_size_per_partition=256, w8a16_peer_comm=comm, bias=bias)
+    m = lm.Fp8LinearMethod((128, 128))
+    y = m.apply(lay, xs, bias if rank == 0 else None)              # vLLM: bias on rank 0 only
+    ref = olin.oracle_linear_fp32(x, w, s, bh) + bias.float()
+    ok = bool(torch.allclose(y.float(), ref, atol=3e-2, rtol=2e-2))
+    # too large for the communicator: plain GEMM + all-reduce, still reduced
+    lay2 = types.SimpleNamespace(**{**vars(lay), "w8a16_peer_comm": types.SimpleNamespace(max_out_elems=16), "bias": None})
+    y2 = m.apply(lay2, xs)
+    ok = ok and bool(torch.allclose(y2.float(), olin.oracle_linear_fp32(x, w, s, bh), atol=3e-2, rtol=2e-2))
+    # a bias handed to a layer that declares none cannot be agreed on: loud failure, on the rank that sees it
+    if rank == 0:
+        try:
+            m.apply(lay2, xs, bias)
+            ok = False
+        except RuntimeError as exc:
+            ok = ok and "could not agree" in str(exc)
+    q.put((rank, ok))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("worker", [_tp_worker, _ep_worker, _comm_failure_worker, _hook_path_worker])
 def test_two_gloo_ranks(worker):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()

@@ -41,6 +41,7 @@ PROTOTYPES = {
     "fp8w8a16_comm_attach_ptr": (c_int, [c_void_p, c_int, c_void_p]),
     "fp8w8a16_comm_base": (c_void_p, [c_void_p]),
     "fp8w8a16_comm_bytes": (c_size_t, [c_void_p]),
+    "fp8w8a16_comm_reset": (c_int, [c_void_p, c_void_p]),
     "fp8w8a16_comm_destroy": (c_int, [c_void_p]),
     "fp8w8a16_linear_allreduce": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                           c_int, c_void_p, c_size_t, c_void_p]),

@@ -596,6 +596,19 @@ void* fp8w8a16_comm_base(const fp8w8a16_comm* comm) { return comm ? comm->c.base
 
 size_t fp8w8a16_comm_bytes(const fp8w8a16_comm* comm) { return comm ? comm->c.bytes : 0; }
 
+int fp8w8a16_comm_reset(fp8w8a16_comm* comm, void* stream) {
+    W8A16_REQUIRE(comm != nullptr, FP8W8A16_ERR_INVALID, "comm_reset: null communicator");
+    Comm& c = comm->c;
+    char* base = c.base[c.rank];
+    W8A16_REQUIRE(base != nullptr, FP8W8A16_ERR_INVALID, "comm_reset: communicator has no local buffer");
+    cudaStream_t st = (cudaStream_t)stream;
+    // control words (launch number, CTAs-done counter), then every packet of both inbox parities: a stale packet whose
+    // tag equals a launch number that is about to be reused would otherwise be taken for a fresh one
+    W8A16_CUDA(cudaMemsetAsync(base, 0, c.part_off, st));
+    W8A16_CUDA(cudaMemsetAsync(base + c.inbox_off, 0, c.bytes - c.inbox_off, st));
+    return 0;
+}
+
 int fp8w8a16_comm_destroy(fp8w8a16_comm* comm) {
     if (comm == nullptr) return 0;
     Comm& c = comm->c;

@@ -40,6 +40,16 @@ inline int check_launch(const char* what) {
     return 0;
 }
 
+// Outcome of a launch call: the launch API's own return code first (an invalid configuration is reported there),
+// then the sticky last-error check that also counts the launch.
+inline int finish_launch(cudaError_t le, const char* what) {
+    if (le != cudaSuccess) {
+        (void)cudaGetLastError();
+        return fail(FP8W8A16_ERR_CUDA, "%s launch failed: %s", what, cudaGetErrorString(le));
+    }
+    return check_launch(what);
+}
+
 // Programmatic dependent launch.  Device side: pdl_trigger() lets the next kernel of the stream begin
 // launching while this one still runs; pdl_wait() blocks until every kernel this one depends on has
 // finished and its writes are visible, and must precede the first access to memory they produce.

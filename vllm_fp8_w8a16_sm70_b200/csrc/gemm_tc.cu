@@ -1136,10 +1136,11 @@ EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-// 2-D row-major tensor [rows, cols] of `elem_bytes` elements, box [box_rows, box_cols].  Encoded
-// descriptors are cached per (address, shape, box): weights keep their address for the life of a
-// model and decode activations usually sit in a reused buffer, so steady-state launches skip the
-// driver call.
+// 2-D row-major tensor [rows, cols] of `elem_bytes` elements, box [box_rows, box_cols].  Encoded descriptors are
+// cached per (address, shape, box).  Weights keep their address for the life of a model: their descriptors live in a
+// map that only grows with the number of distinct weights.  Activation addresses come from the caller's allocator and
+// may be new on every eager call: their descriptors go through a small direct-mapped table (a colliding entry is
+// simply overwritten), so a stream of fresh addresses costs one driver call each and never evicts anything else.
 struct MapKey {
     const void* base;
     uint64_t rows, cols;
@@ -1159,16 +1160,30 @@ struct MapKeyHash {
     }
 };
 
+constexpr size_t kActMapSlots = 1024;
+
 int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t rows, uint64_t cols,
-              uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz) {
+              uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz, bool is_weight) {
     static std::mutex mu;
-    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+    static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> weights;
+    struct Slot {
+        bool used;
+        MapKey key;
+        CUtensorMap map;
+    };
+    static Slot* acts = new Slot[kActMapSlots]();
     const MapKey key{base, rows, cols, box_rows, box_cols, (int)dt, (int)swz};
+    const size_t slot = MapKeyHash()(key) % kActMapSlots;
     {
         std::lock_guard<std::mutex> lock(mu);
-        auto it = cache.find(key);
-        if (it != cache.end()) {
-            *map = it->second;
+        if (is_weight) {
+            auto it = weights.find(key);
+            if (it != weights.end()) {
+                *map = it->second;
+                return 0;
+            }
+        } else if (acts[slot].used && acts[slot].key == key) {
+            *map = acts[slot].map;
             return 0;
         }
     }
@@ -1184,8 +1199,14 @@ int encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const vo
                   (int)r, (unsigned long long)rows, (unsigned long long)cols, box_rows, box_cols);
     {
         std::lock_guard<std::mutex> lock(mu);
-        if (cache.size() >= 8192) cache.clear();
-        cache.emplace(key, *map);
+        if (is_weight) {
+            if (weights.size() >= (1u << 16)) weights.clear();   // far more distinct weights than any model has: start over
+            weights.emplace(key, *map);
+        } else {
+            acts[slot].used = true;
+            acts[slot].key = key;
+            acts[slot].map = *map;
+        }
     }
     return 0;
 }
@@ -1203,9 +1224,9 @@ int launch_cfg(const TcLaunch& L, cudaStream_t st) {
     }
     CUtensorMap map_w, map_x;
     int rc = encode_2d(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, L.w, (uint64_t)L.w_total_rows, (uint64_t)L.p.K, 128, BK,
-                       BK == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+                       BK == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, true);
     if (rc) return rc;
-    rc = encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, L.x, (uint64_t)L.p.M, (uint64_t)L.p.K, BT, 64, CU_TENSOR_MAP_SWIZZLE_128B);
+    rc = encode_2d(&map_x, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, L.x, (uint64_t)L.p.M, (uint64_t)L.p.K, BT, 64, CU_TENSOR_MAP_SWIZZLE_128B, false);
     if (rc) return rc;
     int64_t g = (int64_t)sm_count() * C::kCtasPerSm;
     if (L.max_units < g) g = L.max_units;

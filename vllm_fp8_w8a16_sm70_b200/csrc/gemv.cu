@@ -237,13 +237,14 @@ int launch_gemv(const __half* x, const uint8_t* w, const void* scales, int scale
         const unsigned grid = (unsigned)ctas;
         const __half* xm = x + (int64_t)m0 * K;
         __half* om = out + (int64_t)m0 * N;
+        cudaError_t le = cudaSuccess;
         switch (mc) {
-            case 1: launch_pdl(k_gemv<1>, dim3(grid), dim3(kThreads), 0, st, xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
-            case 2: launch_pdl(k_gemv<2>, dim3(grid), dim3(kThreads), 0, st, xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
-            case 3: launch_pdl(k_gemv<3>, dim3(grid), dim3(kThreads), 0, st, xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
-            default: launch_pdl(k_gemv<4>, dim3(grid), dim3(kThreads), 0, st, xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
+            case 1: le = launch_pdl(k_gemv<1>, dim3(grid), dim3(kThreads), 0, st, xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
+            case 2: le = launch_pdl(k_gemv<2>, dim3(grid), dim3(kThreads), 0, st, xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
+            case 3: le = launch_pdl(k_gemv<3>, dim3(grid), dim3(kThreads), 0, st, xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
+            default: le = launch_pdl(k_gemv<4>, dim3(grid), dim3(kThreads), 0, st, xm, w, scales, scale_dtype, om, partial, tickets, N, K, block_h, Kb, k_chunk, splits, row_groups); break;
         }
-        int rc = check_launch("gemv");
+        int rc = finish_launch(le, "gemv");
         if (rc) return rc;
     }
     return 0;

@@ -367,7 +367,8 @@ template <typename T>
 int launch_topk_t(const T* logits, int M, int E, int topk, int renorm, int* ids, float* weights, cudaStream_t st) {
     const int per_lane = (E + 31) / 32;
     const unsigned blocks = (unsigned)((M + 3) / 4);
-#define W8A16_TOPK(PL) launch_pdl(k_topk_softmax<T, PL>, dim3(blocks), dim3(128), 0, st, logits, M, E, topk, renorm, ids, weights)
+    cudaError_t le = cudaSuccess;
+#define W8A16_TOPK(PL) le = launch_pdl(k_topk_softmax<T, PL>, dim3(blocks), dim3(128), 0, st, logits, M, E, topk, renorm, ids, weights)
     if (per_lane <= 1) W8A16_TOPK(1);
     else if (per_lane <= 2) W8A16_TOPK(2);
     else if (per_lane <= 4) W8A16_TOPK(4);
@@ -375,7 +376,7 @@ int launch_topk_t(const T* logits, int M, int E, int topk, int renorm, int* ids,
     else if (per_lane <= 16) W8A16_TOPK(16);
     else W8A16_TOPK(32);
 #undef W8A16_TOPK
-    return check_launch("moe_topk_softmax");
+    return finish_launch(le, "moe_topk_softmax");
 }
 
 }  // namespace
@@ -399,14 +400,15 @@ int launch_router_t(const __half* x, const W* gate, int M, int E, int H, int top
                     int* ids, float* weights, float* logits_out, cudaStream_t st) {
     const int per_lane = (E + 31) / 32;
     const size_t smem = (size_t)H * sizeof(__half) + (size_t)E * sizeof(float);
-#define W8A16_ROUTER(PL) launch_pdl(k_router_topk<W, PL>, dim3((unsigned)M), dim3(256), smem, st, x, gate, M, E, H, topk, renorm, shared_id, routed_scale, ids, weights, logits_out)
+    cudaError_t le = cudaSuccess;
+#define W8A16_ROUTER(PL) le = launch_pdl(k_router_topk<W, PL>, dim3((unsigned)M), dim3(256), smem, st, x, gate, M, E, H, topk, renorm, shared_id, routed_scale, ids, weights, logits_out)
     if (per_lane <= 1) W8A16_ROUTER(1);
     else if (per_lane <= 2) W8A16_ROUTER(2);
     else if (per_lane <= 4) W8A16_ROUTER(4);
     else if (per_lane <= 8) W8A16_ROUTER(8);
     else W8A16_ROUTER(16);
 #undef W8A16_ROUTER
-    return check_launch("moe_router_topk");
+    return finish_launch(le, "moe_router_topk");
 }
 }  // namespace
 
@@ -428,39 +430,40 @@ int launch_align(const void* ids, int ids_are_i64, int R, const int* expert_map,
                  int* offsets, int* tile_offsets, int* sorted_route, int* inv_pos, cudaStream_t st) {
     W8A16_REQUIRE(E >= 1 && E <= 1024, FP8W8A16_ERR_UNSUPPORTED, "moe_align: E=%d out of range [1,1024]", E);
     const size_t smem = ((size_t)kAlignWarps * E + E + 1) * sizeof(int);
-    if (ids_are_i64) {
-        static bool set64 = false;
-        if (!set64 && smem > 48 * 1024) {
-            W8A16_CUDA(cudaFuncSetAttribute(k_align<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            set64 = true;
-        }
-        launch_pdl(k_align<long long>, dim3(1), dim3(kAlignThreads), smem, st, reinterpret_cast<const long long*>(ids), R, expert_map,
-                   n_global, E, bt, counts, offsets, tile_offsets, sorted_route, inv_pos);
-    } else {
-        static bool set32 = false;
-        if (!set32 && smem > 48 * 1024) {
-            W8A16_CUDA(cudaFuncSetAttribute(k_align<int>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-            set32 = true;
-        }
-        launch_pdl(k_align<int>, dim3(1), dim3(kAlignThreads), smem, st, reinterpret_cast<const int*>(ids), R, expert_map, n_global,
-                   E, bt, counts, offsets, tile_offsets, sorted_route, inv_pos);
+    // Above 48 KiB (E > ~370) the kernel's dynamic shared-memory limit has to be raised.  The attribute belongs to the
+    // (function, device) pair and a later call may need more than an earlier one: remember the largest value set per device.
+    static int set_bytes[2][64] = {};
+    int dev = 0;
+    W8A16_CUDA(cudaGetDevice(&dev));
+    const int which = ids_are_i64 ? 1 : 0;
+    if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || (int)smem > set_bytes[which][dev])) {
+        if (ids_are_i64) W8A16_CUDA(cudaFuncSetAttribute(k_align<long long>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        else W8A16_CUDA(cudaFuncSetAttribute(k_align<int>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < 64) set_bytes[which][dev] = (int)smem;
     }
-    return check_launch("moe_align");
+    cudaError_t le;
+    if (ids_are_i64)
+        le = launch_pdl(k_align<long long>, dim3(1), dim3(kAlignThreads), smem, st, reinterpret_cast<const long long*>(ids), R, expert_map,
+                        n_global, E, bt, counts, offsets, tile_offsets, sorted_route, inv_pos);
+    else
+        le = launch_pdl(k_align<int>, dim3(1), dim3(kAlignThreads), smem, st, reinterpret_cast<const int*>(ids), R, expert_map, n_global,
+                        E, bt, counts, offsets, tile_offsets, sorted_route, inv_pos);
+    return finish_launch(le, "moe_align");
 }
 
 int launch_gather(const __half* x, const int* sorted_route, const float* topk_w, int R, int topk, int H, int weight_on_input,
                   __half* x_sorted, float* w_sorted, cudaStream_t st) {
     W8A16_REQUIRE(H % 8 == 0, FP8W8A16_ERR_UNSUPPORTED, "moe_gather: hidden size %d must be a multiple of 8", H);
     if (R == 0) return 0;
-    launch_pdl(k_gather, dim3((unsigned)((R + 7) / 8)), dim3(256), 0, st, x, sorted_route, topk_w, R, topk, H, weight_on_input, x_sorted, w_sorted);
-    return check_launch("moe_gather");
+    return finish_launch(launch_pdl(k_gather, dim3((unsigned)((R + 7) / 8)), dim3(256), 0, st, x, sorted_route, topk_w, R, topk, H,
+                                    weight_on_input, x_sorted, w_sorted), "moe_gather");
 }
 
 int launch_combine(const __half* y_sorted, const int* inv_pos, int M, int topk, int H, __half* out, cudaStream_t st) {
     W8A16_REQUIRE(H % 8 == 0, FP8W8A16_ERR_UNSUPPORTED, "moe_combine: hidden size %d must be a multiple of 8", H);
     if (M == 0) return 0;
-    launch_pdl(k_combine, dim3((unsigned)M), dim3(256), topk * sizeof(int), st, y_sorted, inv_pos, topk, H, out);
-    return check_launch("moe_combine");
+    return finish_launch(launch_pdl(k_combine, dim3((unsigned)M), dim3(256), topk * sizeof(int), st, y_sorted, inv_pos, topk, H, out),
+                         "moe_combine");
 }
 
 }  // namespace w8a16

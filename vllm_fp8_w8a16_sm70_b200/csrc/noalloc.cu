@@ -29,6 +29,8 @@ constexpr int kMaxDevices = 64;
 // cudaGetSymbolAddress, once per device, with that device current.
 static __device__ __align__(256) unsigned char g_noalloc_scratch[kScratchBytes];
 
+// Filled without a lock: two host threads that race on a device's first call both resolve and store the same
+// address (the symbol has one address per device), so the race is benign.
 void* g_scratch_ptr[kMaxDevices] = {};
 
 // First call on a device: resolve the array's device address.  No allocation happens here, but
@@ -74,7 +76,8 @@ extern "C" int fp8w8a16_linear_noalloc(const uint16_t* x, const uint8_t* w, cons
     // The array keeps whatever the previous call (or an aborted one) left behind.  The partial sums are
     // fully overwritten before they are read; the ticket counters must start at zero, so clear them.
     W8A16_CUDA(cudaMemsetAsync(scratch, 0, kTicketBytes, st));
-    count_variant(FP8W8A16_VARIANT_GEMV);
-    return launch_gemv(reinterpret_cast<const __half*>(x), w, scales, scale_dtype, reinterpret_cast<__half*>(out), M, N, K,
+    rc = launch_gemv(reinterpret_cast<const __half*>(x), w, scales, scale_dtype, reinterpret_cast<__half*>(out), M, N, K,
                        block_h, block_w, scratch, kScratchBytes, st);
+    if (rc == 0) count_variant(FP8W8A16_VARIANT_GEMV);
+    return rc;
 }

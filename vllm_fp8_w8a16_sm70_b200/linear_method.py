@@ -50,32 +50,31 @@ def _apply_2d(layer, x: torch.Tensor, bias, N: int, K: int, scale: torch.Tensor,
         x2d = x2d.contiguous()
     if x2d.shape[-1] != K:
         raise RuntimeError(f"x must be [..., {K}] (got {tuple(x.shape)})")
-    # A row-parallel layer that carries a peer-memory communicator (``layer.w8a16_peer_comm``, set by the integrator
-    # together with ``reduce_results = False``) gets its tensor-parallel all-reduce done inside the GEMM kernel; a
-    # bias would have to be added on one rank only before the reduce (vllm_serve.py:2937-2945), so such calls and
-    # calls larger than the communicator's buffer take the plain path and the caller's own all-reduce.
+    # A row-parallel layer that carries a peer-memory communicator (``layer.w8a16_peer_comm``, attached by the integrator
+    # together with ``reduce_results = False`` and, for a non-default group, ``layer.w8a16_tp_group``) gets its
+    # tensor-parallel reduce done HERE, on every path, so the caller always receives the summed result: fused into the
+    # GEMM kernel when the call fits the communicator, a plain GEMM + all-reduce otherwise.  Every rank must take the
+    # same path (the fused kernel waits for its peers), so the choice uses only facts all ranks share: the token
+    # count, the communicator's size and whether the LAYER has a bias.  vLLM passes the bias argument on rank 0 only
+    # (vllm_serve.py:2937-2945), so the argument itself must not decide.
     comm = getattr(layer, "w8a16_peer_comm", None)
-    if comm is not None and bias is None and x2d.shape[0] * N <= getattr(comm, "max_out_elems", 0):
-        out = ops.w8a16_linear_allreduce(comm, x2d, layer.weight, scale, N, K, block_h, 128)
-        layer.w8a16_reduced = True      # tells the caller that this result is already summed over the ranks
-    else:
-        if compiling:                   # a compiler is tracing: go through the registered op so the graph does not break
-            w8 = layer.weight if layer.weight.dtype == torch.uint8 else layer.weight.view(torch.uint8)
-            out = custom_ops.linear(x2d, w8, scale, N, K, block_h, 128)
+    if comm is not None:
+        layer_bias = getattr(layer, "bias", None) is not None and not getattr(layer, "skip_bias_add", False)
+        if bias is not None and not layer_bias:
+            raise RuntimeError("a bias was passed to a row-parallel layer whose .bias is None: the ranks could not agree on "
+                               "the fused / plain path (set layer.bias on every rank)")
+        fused = (not layer_bias) and (not compiling) and x2d.shape[0] * N <= getattr(comm, "max_out_elems", 0)
+        if fused:
+            out = ops.w8a16_linear_allreduce(comm, x2d, layer.weight, scale, N, K, block_h, 128)
         else:
-            if not x2d.is_cuda:
-                raise RuntimeError(f"x is on {x.device}: the engine runs on CUDA tensors only (there is no CPU path)")
-            # per-layer plan: pointers, shapes and the C entry point resolved once (rebuilt if the tensors were replaced)
-            plan = getattr(layer, "_w8a16_plan", None)
-            if plan is None or not plan.matches(layer.weight, scale) or x2d.device != plan.dev:
-                plan = ops.LinearPlan(layer.weight, scale, N, K, block_h)
-                try:
-                    layer._w8a16_plan = plan
-                except AttributeError:
-                    pass
-            out = plan.run(x2d)
-        if comm is not None:
-            layer.w8a16_reduced = False
+            out = _plain_2d(layer, x2d, scale, N, K, block_h, compiling)
+            if bias is not None:           # rank 0 only: added before the reduce, so it is counted once
+                out = out + bias.to(out.dtype)
+            import torch.distributed as dist
+            dist.all_reduce(out, op=dist.ReduceOp.SUM, group=getattr(layer, "w8a16_tp_group", None))
+        bias = None
+    else:
+        out = _plain_2d(layer, x2d, scale, N, K, block_h, compiling)
     if len(orig_shape) != 2:
         out = out.reshape(orig_shape[:-1] + (N,))
     if bias is not None:
@@ -83,6 +82,24 @@ def _apply_2d(layer, x: torch.Tensor, bias, N: int, K: int, scale: torch.Tensor,
     if out.dtype != x.dtype:
         out = out.to(x.dtype)
     return out
+
+
+def _plain_2d(layer, x2d: torch.Tensor, scale: torch.Tensor, N: int, K: int, block_h: int, compiling: bool) -> torch.Tensor:
+    """This rank's GEMM alone, float16 ``[M, N]``."""
+    if compiling:                   # a compiler is tracing: go through the registered op so the graph does not break
+        w8 = layer.weight if layer.weight.dtype == torch.uint8 else layer.weight.view(torch.uint8)
+        return custom_ops.linear(x2d, w8, scale, N, K, block_h, 128)
+    if not x2d.is_cuda:
+        raise RuntimeError(f"x is on {x2d.device}: the engine runs on CUDA tensors only (there is no CPU path)")
+    # per-layer plan: pointers, shapes and the C entry point resolved once (rebuilt if the tensors were replaced)
+    plan = getattr(layer, "_w8a16_plan", None)
+    if plan is None or not plan.matches(layer.weight, scale) or x2d.device != plan.dev:
+        plan = ops.LinearPlan(layer.weight, scale, N, K, block_h)
+        try:
+            layer._w8a16_plan = plan
+        except AttributeError:
+            pass
+    return plan.run(x2d)
 
 
 class Fp8LinearMethod:

@@ -16,7 +16,9 @@ import torch
 from . import _cabi
 from ._cabi import ALGO_AUTO, ALGO_GEMV, ALGO_TC, SCALE_F16, SCALE_F32  # noqa: F401
 
-_WORKSPACES: dict = {}
+_WORKSPACES: dict = {}      # (device index, raw stream) -> current buffer
+_RETIRED: list = []         # outgrown buffers, kept alive for launches and graphs that still hold their address
+_WS_FLOOR = None
 _LINEAR_WS_BYTES: dict = {}
 _TICKET_BYTES = 65536
 
@@ -53,21 +55,47 @@ def _scale_dtype(s: torch.Tensor) -> int:
     raise RuntimeError(f"scales must be float16 or float32 (got {s.dtype}); cast bf16 scales at load")
 
 
+def _floor_bytes() -> int:
+    """Smallest workspace ever handed out: the largest need of any dense call (the 256-token tile's partial tiles,
+    ~39 MB), so that dense layers never make a workspace grow, whatever order decode and prefill shapes arrive in."""
+    global _WS_FLOOR
+    if _WS_FLOOR is None:
+        _WS_FLOOR = max(int(_cabi.load().fp8w8a16_linear_workspace_bytes(m, 128, 128)) for m in (1, 16, 32, 64, 128, 256))
+    return _WS_FLOOR
+
+
 def workspace(dev: torch.device, nbytes: int, stream: Optional[int] = None) -> torch.Tensor:
-    """Per (device, stream) scratch buffer.  The first 64 KiB hold the kernels' hand-off counters:
-    zero when allocated, left at zero by every kernel.  Grows on demand (a new zeroed buffer)."""
+    """Per (device, stream) scratch buffer.  The first 64 KiB hold the kernels' hand-off counters: zero when
+    allocated, left at zero by every kernel.
+
+    A buffer that has been handed out is NEVER freed: launches already enqueued and CUDA graphs captured earlier
+    keep its address (they write fp32 partial tiles and ticket counters there), so a buffer that is outgrown is
+    retired to a keep-alive list and a larger zeroed one takes its place for new launches.  Creating or growing a
+    workspace while the stream is being captured raises: the new buffer would belong to the graph's private pool.
+    Run each shape once outside capture first (that is what a warm-up does)."""
     key = (dev.index if dev.index is not None else torch.cuda.current_device(), _stream(dev) if stream is None else stream)
     ws = _WORKSPACES.get(key)
     if ws is None or ws.numel() < nbytes:
-        size = max(int(nbytes), 1 << 20)
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError(f"fp8_w8a16: this call needs a {'larger ' if ws is not None else ''}workspace ({int(nbytes)} bytes) "
+                               "on a stream that is being captured; run the same shape once outside the capture first")
+        size = max(int(nbytes), _floor_bytes())
+        if ws is not None:
+            size = max(size, 2 * ws.numel())     # geometric growth: few retired buffers
+            _RETIRED.append(ws)
         ws = torch.zeros(size, dtype=torch.uint8, device=dev)
         _WORKSPACES[key] = ws
     return ws
 
 
 def reset_workspaces() -> None:
-    """Drop all cached workspaces (after a reported device-side timeout the counters may be dirty)."""
-    _WORKSPACES.clear()
+    """After a reported device-side timeout the hand-off counters may be dirty: clear the counter header of every
+    workspace, current and retired, in place.  Nothing is freed (enqueued launches and captured graphs hold the
+    addresses).  Synchronises the device first so that no kernel is using the counters."""
+    if torch.cuda.is_available() and (_WORKSPACES or _RETIRED):
+        torch.cuda.synchronize()
+    for ws in list(_WORKSPACES.values()) + _RETIRED:
+        ws[:_TICKET_BYTES].zero_()
 
 
 class _dev_guard:
@@ -234,9 +262,14 @@ def w8a16_linear_noalloc(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor,
     dev = _require_cuda(x, w, scales, out)
     if x.dtype != torch.float16 or out.dtype != torch.float16:
         raise RuntimeError("x and out must be float16")
+    if x.dim() != 2 or x.shape[1] != K:
+        raise RuntimeError(f"x must be [M, {K}] (got {tuple(x.shape)})")
     M = x.shape[0]
-    if tuple(out.shape) != (M, N) or x.shape[1] != K or w.numel() != N * K:
-        raise RuntimeError("shape mismatch")
+    if tuple(out.shape) != (M, N) or w.numel() != N * K:
+        raise RuntimeError(f"shape mismatch: out {tuple(out.shape)}, weight {w.numel()} elements, expected [{M}, {N}] and N*K={N * K}")
+    nb, kb = -(-N // block_h), -(-K // block_w)
+    if scales.numel() != nb * kb:       # the C ABI sees only a pointer: a short grid would be read out of bounds on the device
+        raise RuntimeError(f"scales have {scales.numel()} elements, expected {nb}x{kb}")
     with _dev_guard(dev):
         _cabi.check(_cabi.load().fp8w8a16_linear_noalloc(x.data_ptr(), w.data_ptr(), scales.data_ptr(), _scale_dtype(scales),
                                                           out.data_ptr(), M, N, K, block_h, block_w, _stream(dev)),
@@ -288,6 +321,12 @@ class PeerComm:
     @property
     def nbytes(self) -> int:
         return int(_cabi.load().fp8w8a16_comm_bytes(self._h))
+
+    def reset(self) -> None:
+        """This rank's part of the collective reset (``fp8w8a16_comm_reset``): launch number back to zero, inbox
+        emptied, on the current stream.  ``parallel.reset_peer_comm`` wraps it in the barriers it needs."""
+        with _dev_guard(self.device):
+            _cabi.check(_cabi.load().fp8w8a16_comm_reset(self._h, _stream(self.device)), "fp8w8a16_comm_reset")
 
     def close(self) -> None:
         if self._h is not None and self._h.value:

@@ -54,17 +54,22 @@ class TensorParallelLinear:
 
     def __init__(self, w_shard: torch.Tensor, s_shard: torch.Tensor, block_h: int, mode: str,
                  group: Optional[dist.ProcessGroup] = None, linear_fn: Optional[Callable] = None,
-                 comm: Optional["ops.PeerComm"] = None):
+                 comm: Optional["ops.PeerComm"] = None, has_bias: bool = False):
         assert mode in ("column", "row")
         self.w, self.s, self.block_h, self.mode, self.group = w_shard, s_shard, block_h, mode, group
         self.N, self.K = int(w_shard.shape[0]), int(w_shard.shape[1])
         self._linear = linear_fn or (lambda x: ops.w8a16_linear(x, self.w, self.s, self.N, self.K, self.block_h, 128))
         self.comm = comm if mode == "row" else None   # fused GEMM + all-reduce over peer memory
+        # whether the LAYER has a bias: the same on every rank, unlike the bias argument of forward (rank 0 only)
+        self.has_bias = bool(has_bias)
 
     def forward(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """column: x [M, K] (replicated) -> [M, N/tp].  row: x [M, K/tp] -> all-reduced [M, N]; the bias is
-        added on rank 0 only before the reduce, as vLLM does."""
-        if self.comm is not None and bias is None and x.shape[0] * self.N <= self.comm_max_elems():
+        added on rank 0 only before the reduce, as vLLM does.  The fused kernel is chosen from rank-invariant facts
+        only (token count, communicator size, ``has_bias``): a rank that went another way would leave its peers waiting."""
+        if bias is not None and self.mode == "row" and self.comm is not None and not self.has_bias:
+            raise RuntimeError("bias passed to a row-parallel layer built with has_bias=False: the ranks could not agree on the path")
+        if self.comm is not None and not self.has_bias and x.shape[0] * self.N <= self.comm_max_elems():
             return ops.w8a16_linear_allreduce(self.comm, x, self.w, self.s, self.N, self.K, self.block_h, 128)
         y = self._linear(x)
         if self.mode == "row":
@@ -75,7 +80,6 @@ class TensorParallelLinear:
         elif bias is not None:
             y = y + bias.to(y.dtype)
         return y
-
 
     def comm_max_elems(self) -> int:
         return getattr(self.comm, "max_out_elems", 0)
@@ -111,6 +115,19 @@ def make_peer_comm(max_out_elems: int, timeout_ms: int = 2000, group: Optional[d
         raise RuntimeError(f"peer-memory communicator could not be set up: {failed}")
     dist.barrier(group=group)
     return comm
+
+
+def reset_peer_comm(comm: "ops.PeerComm", group: Optional[dist.ProcessGroup] = None) -> None:
+    """Collective recovery of the fused all-reduce after the ranks' launch sequences diverged (one rank raised before
+    launching, or a kernel gave up waiting for a peer and the device status word reported bit 128): every rank waits
+    for its own GPU, all meet at a barrier (no fused kernel is in flight anywhere), each resets its launch number and
+    empties its inbox, waits for that, and all meet again before anyone launches."""
+    torch.cuda.synchronize(comm.device)
+    dist.barrier(group=group)
+    comm.reset()
+    torch.cuda.synchronize(comm.device)
+    ops.reset_workspaces()
+    dist.barrier(group=group)
 
 
 # ------------------------------------------------------------------------------------------------
