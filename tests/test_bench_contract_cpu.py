@@ -26,6 +26,8 @@ def test_reference_arm_prints_one_contract_line():
     assert d["cpu_baseline"]["kind"] in ("port", "reference") and d["cpu_baseline"]["cores"] >= 1 and d["cpu_baseline"]["sample"]
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0 and d["e2e"]["value"] == d["value"]
     assert "workload" in d["config"] and "model" not in d["config"]
+    c1 = d["cpu_baseline"]["config1"]          # BASELINE config 1 exactly, dequant and matmul timed separately
+    assert "N=K=4096" in c1["what"] and c1["ms_dequant"] > 0 and c1["ms_matmul"] > 0 and c1["GBps"] > 0
 
 
 @pytest.mark.skipif(torch.cuda.is_available(), reason="only meaningful on a box without a GPU")

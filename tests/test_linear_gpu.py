@@ -111,8 +111,11 @@ def test_tp_shards_through_engine(ops):
 @pytest.mark.parametrize("name,N,K", [("qkv", 7168, 5120), ("o_proj", 5120, 5120), ("down", 5120, 25600), ("gate_up", 51200, 5120)])
 @pytest.mark.parametrize("M", [1, 16, 64, 2048])
 def test_full_size_decode_shapes_on_device(ops, name, N, K, M):
-    """Full decode-sweep shapes (and one prefill batch): compared on the device against the bit-exact dequant kernel followed by an
-    fp32 matmul (the reference's own test method, tests/test_phase5_matmul.py:88-175), plus linearity."""
+    """Full decode-sweep shapes (and one prefill batch): compared on the device against the engine's dequant kernel followed by
+    an fp32 matmul (the reference's own test method, tests/test_phase5_matmul.py:88-175), plus linearity.  Using the engine's own
+    dequantised weight as the reference is sound because that kernel is pinned bit for bit against the CPU oracle and the
+    reference-generated fixtures (test_dequant_gpu.py, full [51200, 5120] included); test_fullsize_gpu.py adds a slab checked
+    against the CPU oracle directly."""
     g = torch.Generator(device="cuda").manual_seed(1)
     w = (torch.randn(N, K, generator=g, device="cuda") * 0.02)
     blocks = w.reshape(N // 128, 128, K // 128, 128)

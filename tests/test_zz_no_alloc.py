@@ -26,7 +26,8 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row(lib):
     from vllm_fp8_w8a16_sm70_b200 import _cabi, ops
     from oracle import linear as olin
     # two different shapes back to back: the second call finds the first one's leftovers in the array
-    cases = [(3, 640, 4096, "block"), (1, 352, 2048, "channel"), (3, 640, 4096, "block")]
+    # (6 tokens: two launches that share the array inside one call; K = 256: too short to split, so no scratch is used at all)
+    cases = [(3, 640, 4096, "block"), (1, 352, 2048, "channel"), (6, 640, 4096, "block"), (2, 384, 256, "block"), (3, 640, 4096, "block")]
     for M, N, K, scheme in cases:
         x, w, s, bh = make_dense(M, N, K, seed=M + N, scheme=scheme)
         xd, wd, sd = x.cuda(), w.cuda(), s.cuda()
@@ -41,6 +42,10 @@ def test_noalloc_matches_workspace_entry_point_twice_in_a_row(lib):
         olin.check_linear(out.cpu(), x, olin.oracle_linear_fp32(x, w, s, bh), K)
     out2 = torch.empty((3, 640), dtype=torch.float16, device="cuda")
     assert torch.equal(ops.w8a16_linear_noalloc(xd, wd, sd, out2, 640, 4096).view(torch.int16), want.view(torch.int16))
+    with pytest.raises(RuntimeError, match="scales have"):        # a short scale grid would be read out of bounds on the device
+        ops.w8a16_linear_noalloc(xd, wd, sd[:-1].contiguous(), out2, 640, 4096)
+    with pytest.raises(RuntimeError, match="x must be"):
+        ops.w8a16_linear_noalloc(xd.reshape(-1), wd, sd, out2, 640, 4096)
 
 
 def test_noalloc_rejects_shapes_beyond_its_scratch(lib):

@@ -158,7 +158,9 @@ class ExpertParallelMoE:
     single-expert route, weight 1) -> all-to-all back -> weighted sum per token on the source rank."""
 
     def __init__(self, w13: torch.Tensor, s13: torch.Tensor, w2: torch.Tensor, s2: torch.Tensor, num_experts: int,
-                 block_h: int = 128, group: Optional[dist.ProcessGroup] = None, expert_fn: Optional[Callable] = None):
+                 block_h: int = 128, group: Optional[dist.ProcessGroup] = None, expert_fn: Optional[Callable] = None,
+                 peer_tokens: int = 0, topk: int = 0, hidden: int = 0):
+        self.peer = None
         self.w13, self.s13, self.w2, self.s2 = w13, s13, w2, s2
         self.num_experts, self.block_h, self.group = num_experts, block_h, group
         self.ep_size = dist.get_world_size(group) if dist.is_initialized() else 1
@@ -167,6 +169,15 @@ class ExpertParallelMoE:
         self._experts = expert_fn or self._engine_experts
         import os
         self.coalesce = os.environ.get("FP8W8A16_EP_COALESCE", "1") != "0"
+
+    def modes(self):
+        """Exchange modes this layer can run: the two NCCL ones, and "peer" when a peer-memory exchange buffer was set up."""
+        return (["peer"] if self.peer is not None else []) + ["allgather", "a2a"]
+
+    def close(self) -> None:
+        if self.peer is not None:
+            self.peer.close()
+            self.peer = None
 
     def _engine_experts(self, rows: torch.Tensor, local_ids: torch.Tensor) -> torch.Tensor:
         ones = torch.ones(rows.shape[0], 1, dtype=torch.float32, device=rows.device)
