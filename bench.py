@@ -258,7 +258,8 @@ def parity_checks(world: int, rank: int, device, fused: bool) -> dict:
     ref = torch_moe_fp32(xt, tw, ids, w13, s13, w2, s2)
     per = E // world
     lo, hi = rank * per, (rank + 1) * per
-    layer = par.ExpertParallelMoE(w13[lo:hi].contiguous(), s13[lo:hi].contiguous(), w2[lo:hi].contiguous(), s2[lo:hi].contiguous(), E)
+    layer = par.ExpertParallelMoE(w13[lo:hi].contiguous(), s13[lo:hi].contiguous(), w2[lo:hi].contiguous(), s2[lo:hi].contiguous(), E,
+                                  peer_tokens=16, topk=topk, hidden=H)
     for mode in layer.modes():
         out = layer.forward(xt, tw, ids, mode=mode).float()
         l2 = float((out - ref).norm() / ref.norm().clamp_min(1e-30))

@@ -219,6 +219,53 @@ int fp8w8a16_moe_gather(const uint16_t* x, const int32_t* sorted_route, const fl
 int fp8w8a16_moe_combine(const uint16_t* y_sorted, const int32_t* inv_pos, int M, int topk, int H, uint16_t* out,
                          void* stream);
 
+/* Expert-parallel MoE layer with the token exchange done by this library's own kernels over peer memory (NVLink):
+ * the experts are partitioned contiguously over the ranks (rank r owns experts [r * E/P, (r + 1) * E/P)), every rank
+ * brings its own tokens.  The reference only tolerates expert parallelism - every rank sees every token, foreign routes
+ * are dropped through expert_map and vLLM reduces afterwards (vllm_serve.py:2237-2243); this is the dispatch / combine
+ * form of the same layer, and its definition of correct is the single-GPU fp8w8a16_moe_forward.
+ *
+ * A handle owns one device allocation per rank (cudaMalloc at create time; calls allocate nothing), mapped into the
+ * peers exactly like a fp8w8a16_comm (export / attach / attach_ptr).  One call = three steps on the caller's stream:
+ *   fp8w8a16_ep_dispatch  route table by destination rank, then every routed row is stored into its owner's inbox with
+ *                         its local expert id, source route index and route weight, followed by a {count, call number}
+ *                         header per destination
+ *   fp8w8a16_ep_experts   bounded wait for every source's header, then align -> gather -> grouped gate/up GEMM with the
+ *                         activation -> grouped down GEMM x route weight on the received rows, then every finished row
+ *                         is stored into its source's return buffer, followed by a flag per source
+ *   fp8w8a16_ep_combine   bounded wait for every owner's flag, then out[m] = sum of the token's routes, in route
+ *                         order, fp32, one rounding (as fp8w8a16_moe_combine)
+ * fp8w8a16_ep_moe_forward runs the three in order.  No host synchronisation, no NCCL: CUDA-graph capturable.
+ * Every rank must make the same sequence of calls.  M may differ between ranks; M_max is the largest M of the call
+ * over all ranks and MUST be passed identically by all of them (it fixes where each source's rows sit in the inbox);
+ * M_max <= max_tokens of fp8w8a16_ep_create.  A wait that runs out (timeout_ms, 0 = 2000) is reported by
+ * fp8w8a16_device_status (bit 256: a header, bit 512: a return flag): the missing source contributes nothing, or
+ * the affected tokens come out as zeros; afterwards every rank must call fp8w8a16_ep_reset (a collective in the
+ * host's hands, like fp8w8a16_comm_reset) before the next call.  The workspace is the caller's, at least
+ * fp8w8a16_ep_workspace_bytes, its first 64 KiB zero on first use (the grouped GEMMs' counters). */
+typedef struct fp8w8a16_ep fp8w8a16_ep;
+int fp8w8a16_ep_create(int rank, int world, int max_tokens, int topk, int hidden, int n_global_experts,
+                       unsigned int timeout_ms, fp8w8a16_ep** ep);
+int fp8w8a16_ep_export(const fp8w8a16_ep* ep, void* handle);
+int fp8w8a16_ep_attach(fp8w8a16_ep* ep, int peer, const void* handle);
+int fp8w8a16_ep_attach_ptr(fp8w8a16_ep* ep, int peer, void* peer_base);
+void* fp8w8a16_ep_base(const fp8w8a16_ep* ep);
+size_t fp8w8a16_ep_bytes(const fp8w8a16_ep* ep);
+int fp8w8a16_ep_reset(fp8w8a16_ep* ep, void* stream);
+int fp8w8a16_ep_destroy(fp8w8a16_ep* ep);
+size_t fp8w8a16_ep_workspace_bytes(const fp8w8a16_ep* ep, int M, int M_max, int num_local_experts, int I);
+int fp8w8a16_ep_dispatch(fp8w8a16_ep* ep, const uint16_t* x, const void* topk_ids, int ids_are_i64,
+                         const float* topk_weights, int M, int M_max, int num_local_experts, int I, void* workspace,
+                         size_t workspace_bytes, void* stream);
+int fp8w8a16_ep_experts(fp8w8a16_ep* ep, const uint8_t* w13, const void* s13, const uint8_t* w2, const void* s2,
+                        int scale_dtype, int M, int M_max, int num_local_experts, int I, int block_h, int activation,
+                        void* workspace, size_t workspace_bytes, void* stream);
+int fp8w8a16_ep_combine(fp8w8a16_ep* ep, const void* topk_ids, int ids_are_i64, uint16_t* out, int M, void* stream);
+int fp8w8a16_ep_moe_forward(fp8w8a16_ep* ep, const uint16_t* x, const void* topk_ids, int ids_are_i64,
+                            const float* topk_weights, const uint8_t* w13, const void* s13, const uint8_t* w2,
+                            const void* s2, int scale_dtype, uint16_t* out, int M, int M_max, int num_local_experts,
+                            int I, int block_h, int activation, void* workspace, size_t workspace_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

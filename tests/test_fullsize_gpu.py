@@ -171,7 +171,9 @@ def test_workspace_growth_does_not_invalidate_a_captured_graph(ops):
         xm = torch.randn(M, 2048, generator=torch.Generator(device="cuda").manual_seed(1), device="cuda").to(torch.float16)
         ids = torch.randint(0, 4, (M, 2), generator=torch.Generator(device="cuda").manual_seed(2), device="cuda", dtype=torch.int32)
         tw = torch.full((M, 2), 0.5, device="cuda")
-        ops.moe_forward(xm, tw, ids, d["w13"].cuda(), d["s13"].cuda(), d["w2"].cuda(), d["s2"].cuda())
+        ew = [d[k].cuda() for k in ("w13", "s13", "w2", "s2")]
+        big = (torch.cat([xm, xm]), torch.cat([tw, tw]), torch.cat([ids, ids]))
+        ops.moe_forward(xm, tw, ids, *ew)
         after = ops._WORKSPACES[(torch.cuda.current_device(), side.cuda_stream)]
         assert after.data_ptr() != before.data_ptr() and after.numel() > before.numel(), "the MoE call was meant to outgrow the workspace"
         assert any(r.data_ptr() == before.data_ptr() for r in ops._RETIRED)
@@ -184,8 +186,7 @@ def test_workspace_growth_does_not_invalidate_a_captured_graph(ops):
         g2 = torch.cuda.CUDAGraph()
         with pytest.raises(RuntimeError, match="being captured"):
             with torch.cuda.graph(g2, stream=side):
-                ops.moe_forward(torch.cat([xm, xm]), torch.cat([tw, tw]), torch.cat([ids, ids]), d["w13"].cuda(), d["s13"].cuda(),
-                                d["w2"].cuda(), d["s2"].cuda())
+                ops.moe_forward(*big, *ew)
     del filler
     olin.check_linear(out.cpu(), x, olin.oracle_linear_fp32(x, w, s, bh), 5120)
     olin.check_linear(out2.cpu(), x2, olin.oracle_linear_fp32(x2, w2, s2, bh), 5120)

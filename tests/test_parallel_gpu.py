@@ -94,12 +94,42 @@ def _worker(rank, world, port, q):
         per = E // world
         lo, hi = rank * per, (rank + 1) * per
         layer = par.ExpertParallelMoE(base["w13"][lo:hi].cuda(), base["s13"][lo:hi].cuda(), base["w2"][lo:hi].cuda(),
-                                      base["s2"][lo:hi].cuda(), E)
+                                      base["s2"][lo:hi].cuda(), E, peer_tokens=16, topk=topk, hidden=H)
         ref = omoe.moe_reference_fp32(d["x"], d["tw"], d["ids"], base["w13"], base["s13"], base["w2"], base["s2"])
-        for mode in ("allgather", "a2a"):
+        assert layer.modes() == ["peer", "allgather", "a2a"]
+        for mode in layer.modes():
             out = layer.forward(d["x"].cuda(), d["tw"].cuda(), d["ids"].cuda(), mode=mode)
             st = omoe.moe_error_stats(out.cpu(), ref)
             res[f"ep_{mode}"] = st["cos"] > 0.9999 and st["l2rel"] < 2e-2
+        # the peer-memory exchange with a different batch on every rank (m_max agreed on), and under CUDA-graph replay
+        m_r = 3 + 2 * rank
+        d2 = make_moe(E, I, H, m_r, topk, seed=40 + rank, invalid_frac=0.2)
+        ref2 = omoe.moe_reference_fp32(d2["x"], d2["tw"], d2["ids"], base["w13"], base["s13"], base["w2"], base["s2"])
+        out2 = layer.forward_peer(d2["x"].cuda(), d2["tw"].cuda(), d2["ids"].cuda(), m_max=3 + 2 * (world - 1))
+        st = omoe.moe_error_stats(out2.cpu(), ref2)
+        res["ep_peer_ragged"] = st["cos"] > 0.9999 and st["l2rel"] < 2e-2
+        xg, twg, idg = d["x"].cuda(), d["tw"].cuda(), d["ids"].cuda()
+        og = torch.empty((M, H), dtype=torch.float16, device="cuda")
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            ops.ep_moe_forward(layer.peer, xg, twg, idg, layer.w13, layer.s13, layer.w2, layer.s2, out=og)      # workspace of this stream exists
+            side.synchronize()
+            dist.barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=side):
+                ops.ep_moe_forward(layer.peer, xg, twg, idg, layer.w13, layer.s13, layer.w2, layer.s2, out=og)
+                ops.ep_moe_forward(layer.peer, xg, twg, idg, layer.w13, layer.s13, layer.w2, layer.s2, out=og)
+            og.zero_()
+            for _ in range(3):
+                g.replay()
+            side.synchronize()
+        torch.cuda.current_stream().wait_stream(side)
+        st = omoe.moe_error_stats(og.cpu(), ref)
+        res["ep_peer_graph"] = st["cos"] > 0.9999 and st["l2rel"] < 2e-2
+        torch.cuda.synchronize()
+        dist.barrier()
+        layer.close()
         res["status"] = ops.device_status() == 0
     finally:
         q.put((rank, res))

@@ -60,6 +60,21 @@ PROTOTYPES = {
     "fp8w8a16_moe_workspace_bytes": (c_size_t, [c_int, c_int, c_int, c_int, c_int]),
     "fp8w8a16_moe_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "fp8w8a16_moe_combine": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "fp8w8a16_ep_create": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, ctypes.c_uint, POINTER(c_void_p)]),
+    "fp8w8a16_ep_export": (c_int, [c_void_p, c_void_p]),
+    "fp8w8a16_ep_attach": (c_int, [c_void_p, c_int, c_void_p]),
+    "fp8w8a16_ep_attach_ptr": (c_int, [c_void_p, c_int, c_void_p]),
+    "fp8w8a16_ep_base": (c_void_p, [c_void_p]),
+    "fp8w8a16_ep_bytes": (c_size_t, [c_void_p]),
+    "fp8w8a16_ep_reset": (c_int, [c_void_p, c_void_p]),
+    "fp8w8a16_ep_destroy": (c_int, [c_void_p]),
+    "fp8w8a16_ep_workspace_bytes": (c_size_t, [c_void_p, c_int, c_int, c_int, c_int]),
+    "fp8w8a16_ep_dispatch": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "fp8w8a16_ep_experts": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                    c_void_p, c_size_t, c_void_p]),
+    "fp8w8a16_ep_combine": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p]),
+    "fp8w8a16_ep_moe_forward": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                        c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
 }
 
 _lib = None

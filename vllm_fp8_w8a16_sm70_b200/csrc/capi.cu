@@ -8,6 +8,7 @@
 #include <new>
 
 #include "common.cuh"
+#include "ep.h"
 #include "gemm_tc.h"
 
 namespace w8a16 {
@@ -63,7 +64,7 @@ int launch_router_topk(const __half* x, const void* gate, int gate_dtype, int M,
 int launch_align(const void* ids, int ids_are_i64, int R, const int* expert_map, int n_global, int E, int bt, int* counts,
                  int* offsets, int* tile_offsets, int* sorted_route, int* inv_pos, cudaStream_t st);
 int launch_gather(const __half* x, const int* sorted_route, const float* topk_w, int R, int topk, int H, int weight_on_input,
-                  __half* x_sorted, float* w_sorted, cudaStream_t st);
+                  __half* x_sorted, float* w_sorted, cudaStream_t st, const int* n_valid = nullptr, int pad_rows = 0);
 int launch_combine(const __half* y_sorted, const int* inv_pos, int M, int topk, int H, __half* out, cudaStream_t st);
 
 namespace {
@@ -256,10 +257,10 @@ struct MoeLayout {
     int bt;
 };
 
-MoeLayout moe_layout(int M, int topk, int E, int H, int I) {
+// Scratch of the grouped pipeline over R routed rows with token tile bt.
+MoeLayout moe_layout_rows(int R, int E, int H, int I, int bt) {
     MoeLayout L;
-    const int R = M * topk;
-    L.bt = token_tile_for(R > 0 ? R : 1, E);
+    L.bt = bt;
     size_t o = kTicketBytes;  // the grouped GEMMs' ticket header sits at the very start
     // the GEMM scratch (tickets + partials) must be one contiguous block: header first, partials
     // right after it; the bookkeeping arrays follow the partials.
@@ -281,6 +282,52 @@ MoeLayout moe_layout(int M, int topk, int E, int H, int I) {
     L.x_sorted = take((size_t)R * H * 2);
     L.h_sorted = take((size_t)R * I * 2);
     L.y_sorted = take((size_t)R * H * 2);
+    L.total = o;
+    return L;
+}
+
+MoeLayout moe_layout(int M, int topk, int E, int H, int I) {
+    const int R = M * topk;
+    return moe_layout_rows(R, E, H, I, token_tile_for(R > 0 ? R : 1, E));
+}
+
+// ---- expert-parallel exchange buffer (see ep.cu) ---------------------------------------------------------------
+struct Ep {
+    EpGeom g;
+    int device, max_tokens, topk, n_global;
+    size_t bytes, off_dest_map;
+    bool ipc_opened[kEpMaxWorld];
+};
+
+// Workspace of one expert-parallel call: the grouped pipeline over world * cap_call received rows first (its ticket
+// header must sit at the start of the workspace), then the receive lists, then the dispatch plan.
+struct EpLayout {
+    MoeLayout moe;
+    size_t counts_in, ids_local, d_counts, d_offsets, d_tiles, d_sorted, d_inv, total;
+    int cap_call, rows_in;
+};
+
+EpLayout ep_layout(const Ep& e, int M, int M_max, int E_local, int I) {
+    EpLayout L;
+    L.cap_call = M_max * e.topk;
+    L.rows_in = e.g.world * L.cap_call;
+    // about as many rows arrive as leave: size the token tile for M * topk rows over the local experts
+    const int r_est = (M > 0 ? M : 1) * e.topk;
+    L.moe = moe_layout_rows(L.rows_in, E_local, e.g.H, I, token_tile_for(r_est, E_local));
+    size_t o = L.moe.total;
+    auto take = [&o](size_t bytes) {
+        const size_t at = o;
+        o += align_up(bytes, 256);
+        return at;
+    };
+    L.counts_in = take(kEpMaxWorld * 4);
+    L.ids_local = take((size_t)L.rows_in * 4);
+    const int R = M * e.topk;
+    L.d_counts = take(kEpMaxWorld * 4);
+    L.d_offsets = take((kEpMaxWorld + 1) * 4);
+    L.d_tiles = take((kEpMaxWorld + 1) * 4);
+    L.d_sorted = take((size_t)(R > 0 ? R : 1) * 4);
+    L.d_inv = take((size_t)(R > 0 ? R : 1) * 4);
     L.total = o;
     return L;
 }
@@ -335,7 +382,13 @@ int fp8w8a16_variant_counts(uint64_t* counts, int n) {
 int fp8w8a16_device_status(int* status, int reset) {
     W8A16_REQUIRE(status != nullptr, FP8W8A16_ERR_INVALID, "device_status: null status pointer");
     W8A16_CUDA(cudaDeviceSynchronize());
-    return tc_read_status(status, reset);
+    int a = 0, b = 0;
+    int rc = tc_read_status(&a, reset);
+    if (rc) return rc;
+    rc = ep_read_status(&b, reset);
+    if (rc) return rc;
+    *status = a | b;
+    return 0;
 }
 
 int fp8w8a16_e4m3_to_fp16(const uint8_t* w, uint16_t* out, int64_t n, void* stream) {
@@ -631,6 +684,242 @@ int fp8w8a16_linear_allreduce(fp8w8a16_comm* comm, const uint16_t* x, const uint
     if (rc) return rc;
     return linear_tc(reinterpret_cast<const __half*>(x), w, scales, scale_dtype, reinterpret_cast<__half*>(out), M, N, K,
                      block_h, workspace, workspace_bytes, (cudaStream_t)stream, &ar);
+}
+
+// ---- expert-parallel MoE over peer memory ------------------------------------------------------------------------
+struct fp8w8a16_ep {
+    w8a16::Ep e;
+};
+
+int fp8w8a16_ep_create(int rank, int world, int max_tokens, int topk, int hidden, int n_global_experts, unsigned int timeout_ms,
+                       fp8w8a16_ep** ep) {
+    W8A16_REQUIRE(ep != nullptr, FP8W8A16_ERR_INVALID, "ep_create: null output pointer");
+    *ep = nullptr;
+    W8A16_REQUIRE(world >= 1 && world <= kEpMaxWorld && rank >= 0 && rank < world, FP8W8A16_ERR_INVALID,
+                  "ep_create: rank %d of world %d (1..%d ranks supported)", rank, world, kEpMaxWorld);
+    W8A16_REQUIRE(max_tokens >= 1 && topk >= 1 && (int64_t)max_tokens * topk <= (1 << 24), FP8W8A16_ERR_INVALID,
+                  "ep_create: max_tokens=%d topk=%d", max_tokens, topk);
+    W8A16_REQUIRE(hidden >= 8 && hidden % 8 == 0, FP8W8A16_ERR_UNSUPPORTED, "ep_create: hidden size %d must be a multiple of 8", hidden);
+    W8A16_REQUIRE(n_global_experts >= world && n_global_experts % world == 0, FP8W8A16_ERR_INVALID,
+                  "ep_create: %d experts do not divide over %d ranks", n_global_experts, world);
+    fp8w8a16_ep* h = new (std::nothrow) fp8w8a16_ep();
+    W8A16_REQUIRE(h != nullptr, FP8W8A16_ERR_CUDA, "ep_create: out of host memory");
+    Ep& e = h->e;
+    memset(&e, 0, sizeof(e));
+    EpGeom& g = e.g;
+    g.world = world;
+    g.rank = rank;
+    g.H = hidden;
+    g.cap = max_tokens * topk;
+    g.experts_per_rank = n_global_experts / world;
+    g.timeout_ms = timeout_ms ? timeout_ms : 2000u;
+    e.max_tokens = max_tokens;
+    e.topk = topk;
+    e.n_global = n_global_experts;
+    size_t o = 0;
+    auto take = [&o](size_t bytes) {
+        const size_t at = o;
+        o += align_up(bytes, 256);
+        return at;
+    };
+    const size_t slots = (size_t)world * g.cap;
+    g.off_ctrl = (int64_t)take(256);
+    g.off_hdr = (int64_t)take(kEpMaxWorld * 8);
+    g.off_rflag = (int64_t)take(kEpMaxWorld * 8);
+    e.off_dest_map = take((size_t)n_global_experts * 4);
+    g.off_meta_e = (int64_t)take(slots * 4);
+    g.off_meta_j = (int64_t)take(slots * 4);
+    g.off_meta_w = (int64_t)take(slots * 4);
+    g.off_rows = (int64_t)take(slots * hidden * 2);
+    g.off_ret = (int64_t)take((size_t)g.cap * hidden * 2);
+    e.bytes = o;
+    cudaError_t ce = cudaGetDevice(&e.device);
+    void* base = nullptr;
+    if (ce == cudaSuccess) ce = cudaMalloc(&base, e.bytes);
+    if (ce == cudaSuccess) ce = cudaMemset(base, 0, e.bytes);
+    if (ce == cudaSuccess) {
+        // expert -> owning rank (contiguous partition): the "expert map" the destination route table is built with
+        int* host_map = new (std::nothrow) int[n_global_experts];
+        if (host_map == nullptr) {
+            ce = cudaErrorMemoryAllocation;
+        } else {
+            for (int x = 0; x < n_global_experts; ++x) host_map[x] = x / g.experts_per_rank;
+            ce = cudaMemcpy(reinterpret_cast<char*>(base) + e.off_dest_map, host_map, (size_t)n_global_experts * 4, cudaMemcpyHostToDevice);
+            delete[] host_map;
+        }
+    }
+    if (ce != cudaSuccess) {
+        if (base) cudaFree(base);
+        delete h;
+        return fail(FP8W8A16_ERR_CUDA, "ep_create: %s", cudaGetErrorString(ce));
+    }
+    g.base[rank] = reinterpret_cast<char*>(base);
+    *ep = h;
+    return 0;
+}
+
+int fp8w8a16_ep_export(const fp8w8a16_ep* ep, void* handle) {
+    W8A16_REQUIRE(ep && handle, FP8W8A16_ERR_INVALID, "ep_export: null pointer");
+    cudaIpcMemHandle_t hd;
+    W8A16_CUDA(cudaIpcGetMemHandle(&hd, ep->e.g.base[ep->e.g.rank]));
+    memcpy(handle, &hd, sizeof(hd));
+    return 0;
+}
+
+int fp8w8a16_ep_attach(fp8w8a16_ep* ep, int peer, const void* handle) {
+    W8A16_REQUIRE(ep && handle, FP8W8A16_ERR_INVALID, "ep_attach: null pointer");
+    Ep& e = ep->e;
+    W8A16_REQUIRE(peer >= 0 && peer < e.g.world && peer != e.g.rank, FP8W8A16_ERR_INVALID, "ep_attach: bad peer %d", peer);
+    W8A16_REQUIRE(e.g.base[peer] == nullptr, FP8W8A16_ERR_INVALID, "ep_attach: peer %d is already attached", peer);
+    cudaIpcMemHandle_t hd;
+    memcpy(&hd, handle, sizeof(hd));
+    void* ptr = nullptr;
+    W8A16_CUDA(cudaIpcOpenMemHandle(&ptr, hd, cudaIpcMemLazyEnablePeerAccess));
+    e.g.base[peer] = reinterpret_cast<char*>(ptr);
+    e.ipc_opened[peer] = true;
+    return 0;
+}
+
+int fp8w8a16_ep_attach_ptr(fp8w8a16_ep* ep, int peer, void* peer_base) {
+    W8A16_REQUIRE(ep && peer_base, FP8W8A16_ERR_INVALID, "ep_attach_ptr: null pointer");
+    Ep& e = ep->e;
+    W8A16_REQUIRE(peer >= 0 && peer < e.g.world && peer != e.g.rank, FP8W8A16_ERR_INVALID, "ep_attach_ptr: bad peer %d", peer);
+    W8A16_REQUIRE(e.g.base[peer] == nullptr, FP8W8A16_ERR_INVALID, "ep_attach_ptr: peer %d is already attached", peer);
+    e.g.base[peer] = reinterpret_cast<char*>(peer_base);
+    e.ipc_opened[peer] = false;
+    return 0;
+}
+
+void* fp8w8a16_ep_base(const fp8w8a16_ep* ep) { return ep ? ep->e.g.base[ep->e.g.rank] : nullptr; }
+
+size_t fp8w8a16_ep_bytes(const fp8w8a16_ep* ep) { return ep ? ep->e.bytes : 0; }
+
+int fp8w8a16_ep_reset(fp8w8a16_ep* ep, void* stream) {
+    W8A16_REQUIRE(ep != nullptr, FP8W8A16_ERR_INVALID, "ep_reset: null handle");
+    Ep& e = ep->e;
+    // call number, kernel counters, headers and return flags; the row buffers need no clearing (they are only read
+    // up to a count that a fresh header announces)
+    W8A16_CUDA(cudaMemsetAsync(e.g.base[e.g.rank], 0, e.off_dest_map, (cudaStream_t)stream));
+    return 0;
+}
+
+int fp8w8a16_ep_destroy(fp8w8a16_ep* ep) {
+    if (ep == nullptr) return 0;
+    Ep& e = ep->e;
+    for (int r = 0; r < e.g.world; ++r)
+        if (r != e.g.rank && e.g.base[r] != nullptr && e.ipc_opened[r]) cudaIpcCloseMemHandle(e.g.base[r]);
+    if (e.g.base[e.g.rank] != nullptr) cudaFree(e.g.base[e.g.rank]);
+    delete ep;
+    return 0;
+}
+
+static int ep_check_call(const fp8w8a16_ep* ep, int M, int M_max, const char* what) {
+    W8A16_REQUIRE(ep != nullptr, FP8W8A16_ERR_INVALID, "%s: null handle", what);
+    const Ep& e = ep->e;
+    for (int r = 0; r < e.g.world; ++r)
+        W8A16_REQUIRE(e.g.base[r] != nullptr, FP8W8A16_ERR_INVALID, "%s: rank %d is not attached", what, r);
+    W8A16_REQUIRE(M >= 0 && M <= M_max && M_max >= 1 && M_max <= e.max_tokens, FP8W8A16_ERR_INVALID,
+                  "%s: M=%d, largest batch of the call %d, buffer built for %d tokens per rank", what, M, M_max, e.max_tokens);
+    return 0;
+}
+
+size_t fp8w8a16_ep_workspace_bytes(const fp8w8a16_ep* ep, int M, int M_max, int num_local_experts, int I) {
+    if (ep == nullptr || M < 0 || M_max < 1 || num_local_experts < 1 || I < 1) return kTicketBytes;
+    return ep_layout(ep->e, M, M_max, num_local_experts, I).total;
+}
+
+int fp8w8a16_ep_dispatch(fp8w8a16_ep* ep, const uint16_t* x, const void* topk_ids, int ids_are_i64, const float* topk_weights,
+                         int M, int M_max, int num_local_experts, int I, void* workspace, size_t workspace_bytes, void* stream) {
+    int rc = ep_check_call(ep, M, M_max, "ep_dispatch");
+    if (rc) return rc;
+    const Ep& e = ep->e;
+    W8A16_REQUIRE(M == 0 || (x && topk_ids && topk_weights), FP8W8A16_ERR_INVALID, "ep_dispatch: null pointer");
+    W8A16_REQUIRE(M == 0 || aligned16(x), FP8W8A16_ERR_INVALID, "ep_dispatch: x must be 16-byte aligned");
+    const EpLayout L = ep_layout(e, M, M_max, num_local_experts, I);
+    W8A16_REQUIRE(workspace != nullptr && workspace_bytes >= L.total, FP8W8A16_ERR_WORKSPACE,
+                  "ep_dispatch: workspace too small (%zu < %zu bytes)", workspace_bytes, L.total);
+    char* ws = reinterpret_cast<char*>(workspace);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int R = M * e.topk;
+    int* d_offsets = reinterpret_cast<int*>(ws + L.d_offsets);
+    int* d_sorted = reinterpret_cast<int*>(ws + L.d_sorted);
+    // route table by destination rank: the align kernel with the expert -> rank map as its expert map
+    rc = launch_align(topk_ids, ids_are_i64, R, reinterpret_cast<const int*>(e.g.base[e.g.rank] + e.off_dest_map), e.n_global, e.g.world, 1,
+                      reinterpret_cast<int*>(ws + L.d_counts), d_offsets, reinterpret_cast<int*>(ws + L.d_tiles), d_sorted,
+                      reinterpret_cast<int*>(ws + L.d_inv), st);
+    if (rc) return rc;
+    return launch_ep_send(reinterpret_cast<const __half*>(x), topk_ids, ids_are_i64, topk_weights, d_sorted, d_offsets, R, e.topk, L.cap_call,
+                          e.g, st);
+}
+
+int fp8w8a16_ep_experts(fp8w8a16_ep* ep, const uint8_t* w13, const void* s13, const uint8_t* w2, const void* s2, int scale_dtype,
+                        int M, int M_max, int num_local_experts, int I, int block_h, int activation, void* workspace,
+                        size_t workspace_bytes, void* stream) {
+    int rc = ep_check_call(ep, M, M_max, "ep_experts");
+    if (rc) return rc;
+    const Ep& e = ep->e;
+    const int H = e.g.H, E = num_local_experts;
+    W8A16_REQUIRE(w13 && s13 && w2 && s2, FP8W8A16_ERR_INVALID, "ep_experts: null pointer");
+    W8A16_REQUIRE(E == e.g.experts_per_rank, FP8W8A16_ERR_INVALID, "ep_experts: %d local experts, the buffer was built for %d", E,
+                  e.g.experts_per_rank);
+    W8A16_REQUIRE(H % 16 == 0 && I > 0 && I % 16 == 0, FP8W8A16_ERR_UNSUPPORTED, "ep_experts: hidden %d and intermediate %d must be multiples of 16", H, I);
+    W8A16_REQUIRE(block_h >= 1, FP8W8A16_ERR_INVALID, "ep_experts: block_h=%d", block_h);
+    W8A16_REQUIRE(activation == FP8W8A16_ACT_SILU || activation == FP8W8A16_ACT_GELU, FP8W8A16_ERR_UNSUPPORTED,
+                  "ep_experts: activation %d is not SiLU (1) or GELU (2)", activation);
+    W8A16_REQUIRE(scale_dtype == FP8W8A16_SCALE_F16 || scale_dtype == FP8W8A16_SCALE_F32, FP8W8A16_ERR_INVALID, "ep_experts: unknown scale dtype %d", scale_dtype);
+    const EpLayout L = ep_layout(e, M, M_max, E, I);
+    W8A16_REQUIRE(workspace != nullptr && workspace_bytes >= L.total && aligned16(workspace), FP8W8A16_ERR_WORKSPACE,
+                  "ep_experts: workspace too small or misaligned (%zu < %zu bytes)", workspace_bytes, L.total);
+    char* ws = reinterpret_cast<char*>(workspace);
+    cudaStream_t st = (cudaStream_t)stream;
+    const MoeLayout& ML = L.moe;
+    int* counts_in = reinterpret_cast<int*>(ws + L.counts_in);
+    int* ids_local = reinterpret_cast<int*>(ws + L.ids_local);
+    int* counts = reinterpret_cast<int*>(ws + ML.counts);
+    int* offsets = reinterpret_cast<int*>(ws + ML.offsets);
+    int* tile_offsets = reinterpret_cast<int*>(ws + ML.tile_offsets);
+    int* sorted_route = reinterpret_cast<int*>(ws + ML.sorted_route);
+    int* inv_pos = reinterpret_cast<int*>(ws + ML.inv_pos);
+    float* w_sorted = reinterpret_cast<float*>(ws + ML.w_sorted);
+    __half* x_sorted = reinterpret_cast<__half*>(ws + ML.x_sorted);
+    __half* h_sorted = reinterpret_cast<__half*>(ws + ML.h_sorted);
+    __half* y_sorted = reinterpret_cast<__half*>(ws + ML.y_sorted);
+    const char* mine = e.g.base[e.g.rank];
+    const int Rin = L.rows_in;
+    rc = launch_ep_recv(L.cap_call, counts_in, ids_local, e.g, st);
+    if (rc) return rc;
+    rc = launch_align(ids_local, 0, Rin, nullptr, E, E, ML.bt, counts, offsets, tile_offsets, sorted_route, inv_pos, st);
+    if (rc) return rc;
+    // every received row is one route of its own (top-1 view of the inbox); its weight came with it
+    rc = launch_gather(reinterpret_cast<const __half*>(mine + e.g.off_rows), sorted_route, reinterpret_cast<const float*>(mine + e.g.off_meta_w),
+                       Rin, 1, H, 0, x_sorted, w_sorted, st, offsets + E, ML.bt);
+    if (rc) return rc;
+    rc = grouped_gemm(x_sorted, w13, s13, scale_dtype, h_sorted, nullptr, offsets, tile_offsets, Rin, E, I, H, block_h, activation, ML.bt,
+                      ws + ML.gemm_ws, ML.gemm_ws_bytes, st);
+    if (rc) return rc;
+    rc = grouped_gemm(h_sorted, w2, s2, scale_dtype, y_sorted, w_sorted, offsets, tile_offsets, Rin, E, H, I, block_h, 0, ML.bt,
+                      ws + ML.gemm_ws, ML.gemm_ws_bytes, st);
+    if (rc) return rc;
+    return launch_ep_return(y_sorted, inv_pos, counts_in, L.cap_call, e.g, st);
+}
+
+int fp8w8a16_ep_combine(fp8w8a16_ep* ep, const void* topk_ids, int ids_are_i64, uint16_t* out, int M, void* stream) {
+    int rc = ep_check_call(ep, M, M > 0 ? M : 1, "ep_combine");
+    if (rc) return rc;
+    W8A16_REQUIRE(M == 0 || (topk_ids && out && aligned16(out)), FP8W8A16_ERR_INVALID, "ep_combine: null or misaligned pointer");
+    return launch_ep_combine(topk_ids, ids_are_i64, M, ep->e.topk, reinterpret_cast<__half*>(out), ep->e.g, (cudaStream_t)stream);
+}
+
+int fp8w8a16_ep_moe_forward(fp8w8a16_ep* ep, const uint16_t* x, const void* topk_ids, int ids_are_i64, const float* topk_weights,
+                            const uint8_t* w13, const void* s13, const uint8_t* w2, const void* s2, int scale_dtype, uint16_t* out,
+                            int M, int M_max, int num_local_experts, int I, int block_h, int activation, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+    int rc = fp8w8a16_ep_dispatch(ep, x, topk_ids, ids_are_i64, topk_weights, M, M_max, num_local_experts, I, workspace, workspace_bytes, stream);
+    if (rc) return rc;
+    rc = fp8w8a16_ep_experts(ep, w13, s13, w2, s2, scale_dtype, M, M_max, num_local_experts, I, block_h, activation, workspace,
+                             workspace_bytes, stream);
+    if (rc) return rc;
+    return fp8w8a16_ep_combine(ep, topk_ids, ids_are_i64, out, M, stream);
 }
 
 }  // extern "C"

@@ -273,15 +273,19 @@ k_align(const IdT* __restrict__ ids, int R, const int* __restrict__ expert_map, 
 // ------------------------------------------------------------------------------------------------
 // gather: x_sorted[pos] = x[route / topk] (optionally x route weight), w_sorted[pos] = weight[route].
 // One warp per sorted row, 16-byte copies.  Rows past the valid count are zero-filled so that the
-// token tiles of the grouped GEMM never read uninitialised memory.
+// token tiles of the grouped GEMM never read uninitialised memory.  When most of the R slots are known to be empty (the
+// expert-parallel inbox: R is a capacity), `n_valid` points at the valid-row count and only `pad_rows` rows past it
+// - what the last token tile can reach - are zero-filled.
 // ------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256)
 k_gather(const __half* __restrict__ x, const int* __restrict__ sorted_route, const float* __restrict__ topk_w, int R,
-         int topk, int H, int weight_on_input, __half* __restrict__ x_sorted, float* __restrict__ w_sorted) {
+         int topk, int H, int weight_on_input, __half* __restrict__ x_sorted, float* __restrict__ w_sorted,
+         const int* __restrict__ n_valid, int pad_rows) {
     pdl_trigger();
     pdl_wait();
     const int pos = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (pos >= R) return;
+    if (n_valid != nullptr && pos >= *n_valid + pad_rows) return;
     const int route = sorted_route[pos];
     uint4* dst = reinterpret_cast<uint4*>(x_sorted + (int64_t)pos * H);
     const int vecs = H >> 3;
@@ -452,11 +456,11 @@ int launch_align(const void* ids, int ids_are_i64, int R, const int* expert_map,
 }
 
 int launch_gather(const __half* x, const int* sorted_route, const float* topk_w, int R, int topk, int H, int weight_on_input,
-                  __half* x_sorted, float* w_sorted, cudaStream_t st) {
+                  __half* x_sorted, float* w_sorted, cudaStream_t st, const int* n_valid, int pad_rows) {
     W8A16_REQUIRE(H % 8 == 0, FP8W8A16_ERR_UNSUPPORTED, "moe_gather: hidden size %d must be a multiple of 8", H);
     if (R == 0) return 0;
     return finish_launch(launch_pdl(k_gather, dim3((unsigned)((R + 7) / 8)), dim3(256), 0, st, x, sorted_route, topk_w, R, topk, H,
-                                    weight_on_input, x_sorted, w_sorted), "moe_gather");
+                                    weight_on_input, x_sorted, w_sorted, n_valid, pad_rows), "moe_gather");
 }
 
 int launch_combine(const __half* y_sorted, const int* inv_pos, int M, int topk, int H, __half* out, cudaStream_t st) {

@@ -542,6 +542,107 @@ def moe_forward(x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Ten
     return out
 
 
+class EpComm:
+    """One rank's end of the expert-parallel exchange buffer (``fp8w8a16_ep_*``): an inbox for routed rows, a return
+    buffer for finished rows and their headers / flags, mapped into the peers through CUDA IPC like a ``PeerComm``."""
+
+    def __init__(self, rank: int, world: int, max_tokens: int, topk: int, hidden: int, num_experts: int, timeout_ms: int = 2000,
+                 device: Optional[torch.device] = None):
+        self.rank, self.world, self.max_tokens, self.topk, self.hidden, self.num_experts = rank, world, max_tokens, topk, hidden, num_experts
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
+        if self.device.type != "cuda":
+            raise RuntimeError("EpComm needs a CUDA device (there is no CPU path)")
+        self._h = ctypes.c_void_p()
+        with _dev_guard(self.device):
+            _cabi.check(_cabi.load().fp8w8a16_ep_create(rank, world, max_tokens, topk, hidden, num_experts, timeout_ms,
+                                                       ctypes.byref(self._h)), "fp8w8a16_ep_create")
+
+    def handle(self) -> bytes:
+        buf = ctypes.create_string_buffer(_cabi.COMM_HANDLE_BYTES)
+        with _dev_guard(self.device):
+            _cabi.check(_cabi.load().fp8w8a16_ep_export(self._h, buf), "fp8w8a16_ep_export")
+        return buf.raw
+
+    def attach(self, peer: int, handle: bytes) -> None:
+        buf = ctypes.create_string_buffer(handle, _cabi.COMM_HANDLE_BYTES)
+        with _dev_guard(self.device):
+            _cabi.check(_cabi.load().fp8w8a16_ep_attach(self._h, peer, buf), "fp8w8a16_ep_attach")
+
+    def attach_ptr(self, peer: int, base: int) -> None:
+        _cabi.check(_cabi.load().fp8w8a16_ep_attach_ptr(self._h, peer, base), "fp8w8a16_ep_attach_ptr")
+
+    @property
+    def base(self) -> int:
+        return int(_cabi.load().fp8w8a16_ep_base(self._h) or 0)
+
+    @property
+    def nbytes(self) -> int:
+        return int(_cabi.load().fp8w8a16_ep_bytes(self._h))
+
+    def reset(self) -> None:
+        with _dev_guard(self.device):
+            _cabi.check(_cabi.load().fp8w8a16_ep_reset(self._h, _stream(self.device)), "fp8w8a16_ep_reset")
+
+    def close(self) -> None:
+        if self._h is not None and self._h.value:
+            with _dev_guard(self.device):
+                _cabi.load().fp8w8a16_ep_destroy(self._h)
+            self._h = None
+
+
+def _ep_args(ep: EpComm, w13: torch.Tensor, w2: torch.Tensor, s13: torch.Tensor, s2: torch.Tensor, block_h: int):
+    E, two_i, H = w13.shape
+    I = two_i // 2
+    if H != ep.hidden or tuple(w2.shape) != (E, H, I) or E * ep.world != ep.num_experts:
+        raise RuntimeError(f"expert shapes {tuple(w13.shape)} / {tuple(w2.shape)} do not match the exchange buffer "
+                           f"(hidden {ep.hidden}, {ep.num_experts} experts over {ep.world} ranks)")
+    if s13.dtype != s2.dtype:
+        raise RuntimeError("w13 and w2 scales must share a dtype")
+    if s13.numel() != E * (-(-two_i // block_h)) * (-(-H // 128)) or s2.numel() != E * (-(-H // block_h)) * (-(-I // 128)):
+        raise RuntimeError("scale grid size does not match the weights and block_h")
+    return E, I
+
+
+def ep_moe_forward(ep: EpComm, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor, w13: torch.Tensor, s13: torch.Tensor,
+                   w2: torch.Tensor, s2: torch.Tensor, block_h: int = 128, activation: str = "silu", m_max: Optional[int] = None,
+                   out: Optional[torch.Tensor] = None, phase: str = "all") -> Optional[torch.Tensor]:
+    """Expert-parallel routed MoE layer over peer memory: this rank's tokens ``x [M, H]`` with GLOBAL expert ids, this
+    rank's expert slice ``w13 [E/P, 2I, H]`` / ``w2 [E/P, H, I]``.  ``m_max`` is the largest token count any rank brings
+    to this call and must be the same on every rank (default: this rank's M, i.e. equal batches).  ``phase`` runs one
+    step only ("dispatch", "experts", "combine") - used to drive several ranks from one process in tests."""
+    w13, w2 = _as_u8(w13), _as_u8(w2)
+    dev = _require_cuda(x, topk_weights, topk_ids, w13, s13, w2, s2)
+    if x.dtype != torch.float16 or x.dim() != 2 or x.shape[1] != ep.hidden:
+        raise RuntimeError(f"x must be float16 [M, {ep.hidden}]")
+    if activation not in _ACTIVATIONS:
+        raise NotImplementedError(f"unsupported MoE activation {activation!r} (silu or gelu)")
+    if topk_weights.dtype != torch.float32 or topk_ids.dtype not in (torch.int32, torch.int64):
+        raise RuntimeError("topk_weights must be float32 and topk_ids int32 or int64")
+    M = x.shape[0]
+    if topk_ids.numel() != M * ep.topk or topk_weights.numel() != M * ep.topk:
+        raise RuntimeError(f"topk_ids / topk_weights must be [M, {ep.topk}]")
+    E, I = _ep_args(ep, w13, w2, s13, s2, block_h)
+    m_max = M if m_max is None else int(m_max)
+    if not (1 <= m_max <= ep.max_tokens and M <= m_max):
+        raise RuntimeError(f"m_max={m_max} must cover M={M} and fit the buffer's {ep.max_tokens} tokens per rank")
+    lib = _cabi.load()
+    i64 = 1 if topk_ids.dtype == torch.int64 else 0
+    if out is None and phase in ("all", "combine"):
+        out = torch.empty((M, ep.hidden), dtype=torch.float16, device=dev)
+    with _dev_guard(dev):
+        st = _stream(dev)
+        ws = workspace(dev, lib.fp8w8a16_ep_workspace_bytes(ep._h, M, m_max, E, I), st)
+        if phase in ("all", "dispatch"):
+            _cabi.check(lib.fp8w8a16_ep_dispatch(ep._h, x.data_ptr(), topk_ids.data_ptr(), i64, topk_weights.data_ptr(), M, m_max, E, I,
+                                                 ws.data_ptr(), ws.numel(), st), "fp8w8a16_ep_dispatch")
+        if phase in ("all", "experts"):
+            _cabi.check(lib.fp8w8a16_ep_experts(ep._h, w13.data_ptr(), s13.data_ptr(), w2.data_ptr(), s2.data_ptr(), _scale_dtype(s13), M, m_max,
+                                                E, I, block_h, _ACTIVATIONS[activation], ws.data_ptr(), ws.numel(), st), "fp8w8a16_ep_experts")
+        if phase in ("all", "combine"):
+            _cabi.check(lib.fp8w8a16_ep_combine(ep._h, topk_ids.data_ptr(), i64, out.data_ptr(), M, st), "fp8w8a16_ep_combine")
+    return out
+
+
 def device_status(reset: bool = True) -> int:
     """Sticky device status word (0 = healthy).  Synchronises the device."""
     return _cabi.device_status(reset)

@@ -85,15 +85,15 @@ class TensorParallelLinear:
         return getattr(self.comm, "max_out_elems", 0)
 
 
-def make_peer_comm(max_out_elems: int, timeout_ms: int = 2000, group: Optional[dist.ProcessGroup] = None) -> "ops.PeerComm":
-    """Collective: every rank of ``group`` creates its communicator buffer on its current CUDA device, the IPC handles
-    travel through ``all_gather_object`` and every rank maps every peer.  Failures are agreed on: if any rank cannot
-    create or map a buffer, every rank closes what it has and raises, so the callers stay in step.  Ends with a
-    barrier so that no rank launches before all mappings exist."""
+def _make_shared(create: Callable, what: str, group: Optional[dist.ProcessGroup]):
+    """Collective set-up of a peer-mapped buffer: every rank of ``group`` creates its buffer on its current CUDA device,
+    the IPC handles travel through ``all_gather_object`` and every rank maps every peer.  Failures are agreed on: if any
+    rank cannot create or map a buffer, every rank closes what it has and raises, so the callers stay in step.  Ends with
+    a barrier so that no rank launches before all mappings exist."""
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     comm, err = None, None
     try:
-        comm = ops.PeerComm(rank, world, max_out_elems, timeout_ms)
+        comm = create(rank, world)
         mine = comm.handle()
     except Exception as exc:  # noqa: BLE001 - re-raised on every rank below
         mine, err = None, repr(exc)
@@ -112,13 +112,25 @@ def make_peer_comm(max_out_elems: int, timeout_ms: int = 2000, group: Optional[d
     if failed:
         if comm is not None:
             comm.close()
-        raise RuntimeError(f"peer-memory communicator could not be set up: {failed}")
+        raise RuntimeError(f"{what} could not be set up: {failed}")
     dist.barrier(group=group)
     return comm
 
 
-def reset_peer_comm(comm: "ops.PeerComm", group: Optional[dist.ProcessGroup] = None) -> None:
-    """Collective recovery of the fused all-reduce after the ranks' launch sequences diverged (one rank raised before
+def make_peer_comm(max_out_elems: int, timeout_ms: int = 2000, group: Optional[dist.ProcessGroup] = None) -> "ops.PeerComm":
+    """The communicator of the fused row-parallel GEMM + all-reduce (collective; raises on every rank or on none)."""
+    return _make_shared(lambda rank, world: ops.PeerComm(rank, world, max_out_elems, timeout_ms), "peer-memory communicator", group)
+
+
+def make_ep_comm(max_tokens: int, topk: int, hidden: int, num_experts: int, timeout_ms: int = 2000,
+                 group: Optional[dist.ProcessGroup] = None) -> "ops.EpComm":
+    """The exchange buffer of the expert-parallel MoE layer (collective; raises on every rank or on none)."""
+    return _make_shared(lambda rank, world: ops.EpComm(rank, world, max_tokens, topk, hidden, num_experts, timeout_ms),
+                        "expert-parallel exchange buffer", group)
+
+
+def reset_peer_comm(comm, group: Optional[dist.ProcessGroup] = None) -> None:
+    """Collective recovery of a peer-memory communicator (``PeerComm`` or ``EpComm``) after the ranks' launch sequences diverged (one rank raised before
     launching, or a kernel gave up waiting for a peer and the device status word reported bit 128): every rank waits
     for its own GPU, all meet at a barrier (no fused kernel is in flight anywhere), each resets its launch number and
     empties its inbox, waits for that, and all meet again before anyone launches."""
@@ -169,6 +181,9 @@ class ExpertParallelMoE:
         self._experts = expert_fn or self._engine_experts
         import os
         self.coalesce = os.environ.get("FP8W8A16_EP_COALESCE", "1") != "0"
+        # peer_tokens > 0: set up the peer-memory exchange (collective) for up to that many tokens per rank and call
+        if peer_tokens > 0 and self.ep_size > 1 and expert_fn is None and w13.is_cuda:
+            self.peer = make_ep_comm(peer_tokens, topk, hidden or int(w13.shape[2]), num_experts, group=group)
 
     def modes(self):
         """Exchange modes this layer can run: the two NCCL ones, and "peer" when a peer-memory exchange buffer was set up."""
@@ -191,10 +206,26 @@ class ExpertParallelMoE:
         synchronisation, CUDA-graph capturable; the right choice for decode batches), "auto" = all-gather up to
         4096 tokens in flight, all-to-all above."""
         if mode == "auto":
-            mode = "allgather" if x.shape[0] * self.ep_size <= 4096 else "a2a"
+            if self.peer is not None and x.shape[0] <= self.peer.max_tokens:
+                mode = "peer"
+            else:
+                mode = "allgather" if x.shape[0] * self.ep_size <= 4096 else "a2a"
+        if mode == "peer":
+            if self.peer is None:
+                raise RuntimeError("this layer was built without a peer-memory exchange buffer (peer_tokens=0)")
+            return self.forward_peer(x, topk_weights, topk_ids)
         if mode == "allgather" and self.ep_size > 1 and self._experts == self._engine_experts:
             return self.forward_allgather(x, topk_weights, topk_ids)
         return self.forward_a2a(x, topk_weights, topk_ids)
+
+    def forward_peer(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor, m_max: Optional[int] = None) -> torch.Tensor:
+        """Dispatch / experts / combine by the library's own kernels over peer memory: only routed rows travel, nothing is
+        read back on the host, no NCCL call (CUDA-graph capturable).  ``m_max``: the largest token count of any rank in
+        this call, identical on all ranks (default: equal batches)."""
+        ids = topk_ids if topk_ids.dtype in (torch.int32, torch.int64) else topk_ids.to(torch.int32)
+        tw = topk_weights if topk_weights.dtype == torch.float32 else topk_weights.float()
+        return ops.ep_moe_forward(self.peer, x.contiguous(), tw.contiguous(), ids.contiguous(), self.w13, self.s13, self.w2, self.s2,
+                                  block_h=self.block_h, m_max=m_max)
 
     def forward_allgather(self, x: torch.Tensor, topk_weights: torch.Tensor, topk_ids: torch.Tensor) -> torch.Tensor:
         """Every rank brings M tokens (the same M on all ranks).  all-gather -> [P*M] tokens; this rank's experts
