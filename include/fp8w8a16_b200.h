@@ -151,6 +151,26 @@ int fp8w8a16_linear_allreduce(fp8w8a16_comm* comm, const uint16_t* x, const uint
                               int scale_dtype, uint16_t* out, int M, int N, int K, int block_h, int block_w,
                               void* workspace, size_t workspace_bytes, void* stream);
 
+/* The two steps that follow a row-parallel projection (o_proj, down_proj) in a decoder layer, which in the reference's
+ * deployment are vLLM's: the residual add and the RMSNorm of fused_add_rms_norm, run after apply() and the tensor-parallel
+ * reduce (call site mirrored at vllm_serve.py:2922-2959).
+ *   fp8w8a16_linear_residual / fp8w8a16_linear_allreduce_residual: as fp8w8a16_linear (tensor-core path, any M) and
+ *     fp8w8a16_linear_allreduce with out = FP16(fp32 result + residual): the residual stream (FP16 [M,N]) joins in the
+ *     GEMM's epilogue - in the fused form after the cross-rank sum - before the one rounding.  out may alias residual.
+ *     A NULL residual in the all-reduce form gives fp8w8a16_linear_allreduce.
+ *   fp8w8a16_add_rmsnorm: z = x + residual (fp32 sum, one FP16 rounding; residual may be NULL when it was already added
+ *     in the epilogue above: z = x), residual_out = z (may alias residual or x; may be NULL when residual is NULL),
+ *     out = FP16(z * rsqrt(mean(z^2) + eps)) * weight with weight FP16 [N] (vLLM's kernel order: the norm of the rounded z,
+ *     FP16 product).  One CTA per row, N a multiple of 8, at most 32768. */
+int fp8w8a16_linear_residual(const uint16_t* x, const uint8_t* w, const void* scales, int scale_dtype, const uint16_t* residual,
+                             uint16_t* out, int M, int N, int K, int block_h, int block_w, void* workspace,
+                             size_t workspace_bytes, void* stream);
+int fp8w8a16_linear_allreduce_residual(fp8w8a16_comm* comm, const uint16_t* x, const uint8_t* w, const void* scales,
+                                       int scale_dtype, const uint16_t* residual, uint16_t* out, int M, int N, int K,
+                                       int block_h, int block_w, void* workspace, size_t workspace_bytes, void* stream);
+int fp8w8a16_add_rmsnorm(const uint16_t* x, const uint16_t* residual, const uint16_t* weight, float eps, uint16_t* out,
+                         uint16_t* residual_out, int M, int N, void* stream);
+
 /* Router: logits [M,E] -> topk_ids int32 [M,topk] (descending, ties to the lowest expert id),
  * topk_weights fp32 [M,topk] = softmax probabilities of the picks (renormalize != 0: divided by
  * their sum).  Stands in for vLLM's fused_topk, whose output the reference's MoE apply consumes

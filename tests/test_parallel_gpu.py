@@ -63,6 +63,24 @@ def _worker(rank, world, port, q):
             same_ok = same_ok and all(torch.equal(both[0], b) for b in both[1:])
         res["fused_allreduce"] = fused_ok
         res["fused_allreduce_identical_on_all_ranks"] = same_ok
+        # the residual stream joins the cross-rank sum inside the kernel (cluster and stream-K shapes), in place
+        rok = True
+        for ci, (Mf, Nf, Kf) in enumerate([(8, 5120, 5120), (40, 5120, 2048)]):
+            xf, wf, sf, bhf = make_dense(Mf, Nf, Kf, seed=60 + ci)
+            resid = torch.randn(Mf, Nf, generator=torch.Generator().manual_seed(70 + ci)).to(torch.float16)
+            wsh, ssh = par.shard_row_parallel(wf, sf, world, rank)
+            k_per = Kf // world
+            xs = xf[:, rank * k_per:(rank + 1) * k_per].contiguous().cuda()
+            lay = par.TensorParallelLinear(wsh.cuda(), ssh.cuda(), bhf, "row", comm=comm)
+            ref = olin.oracle_linear_fp32(xf, wf, sf, bhf) + resid.float()
+            dist.barrier()
+            rbuf = resid.cuda()
+            yr = lay.forward(xs, residual=rbuf)
+            stf = olin.error_stats(yr.cpu(), ref)
+            rok = rok and stf["rel_rms"] < 1.5e-2 and stf["finite"]
+            nccl = par.TensorParallelLinear(wsh.cuda(), ssh.cuda(), bhf, "row").forward(xs, residual=rbuf)
+            rok = rok and olin.error_stats(nccl.cpu(), ref)["rel_rms"] < 1.5e-2
+        res["fused_allreduce_residual"] = rok
         # CUDA-graph replay of a fused call (the launch counter lives on the device)
         xf, wf, sf, bhf = make_dense(4, 5120, 5120, seed=31)
         wsh, ssh = par.shard_row_parallel(wf, sf, world, rank)

@@ -10,7 +10,10 @@ import ctypes
 from ctypes import c_int, c_int32, c_int64, c_size_t, c_void_p, c_char_p, POINTER
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "lib" / "libfp8w8a16_b200.so"
+import os
+
+# FP8W8A16_LIBRARY names another build of the library (a debug or instrumented build, say); default: the in-tree one.
+LIB_PATH = Path(os.environ.get("FP8W8A16_LIBRARY") or (Path(__file__).resolve().parent / "lib" / "libfp8w8a16_b200.so"))
 
 OK = 0
 ERR_INVALID, ERR_CUDA, ERR_UNSUPPORTED, ERR_WORKSPACE, ERR_DEVICE = -1, -2, -3, -4, -5
@@ -45,6 +48,11 @@ PROTOTYPES = {
     "fp8w8a16_comm_destroy": (c_int, [c_void_p]),
     "fp8w8a16_linear_allreduce": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                                           c_int, c_void_p, c_size_t, c_void_p]),
+    "fp8w8a16_linear_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                         c_void_p, c_size_t, c_void_p]),
+    "fp8w8a16_linear_allreduce_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                                   c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "fp8w8a16_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, ctypes.c_float, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "fp8w8a16_moe_topk_softmax": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "fp8w8a16_moe_router_topk": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, ctypes.c_float,
                                          c_void_p, c_void_p, c_void_p, c_void_p]),

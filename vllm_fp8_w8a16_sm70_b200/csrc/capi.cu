@@ -54,6 +54,8 @@ int launch_e4m3_to_fp16(const uint8_t* in, __half* out, int64_t n, cudaStream_t 
 int launch_e4m3_to_fp16_scaled(const uint8_t* in, const __half* scales, __half* out, int64_t n, int64_t group, cudaStream_t st);
 int launch_dequant_block(const uint8_t* w, const void* scales, int scale_dtype, __half* out, int N, int K, int block_h,
                          int block_w, cudaStream_t st);
+int launch_add_rmsnorm(const __half* x, const __half* residual, const __half* weight, float eps, __half* out, __half* residual_out,
+                       int M, int N, cudaStream_t st);
 size_t gemv_workspace_bytes(int M, int N, int K);
 int launch_gemv(const __half* x, const uint8_t* w, const void* scales, int scale_dtype, __half* out, int M, int N, int K,
                 int block_h, int block_w, void* workspace, size_t workspace_bytes, cudaStream_t st);
@@ -79,17 +81,8 @@ size_t tc_dense_workspace_bytes(int M, int N, int K) {
     return tc_workspace_bytes(dense_token_tile(M), false);
 }
 
-// Token tile of the tensor-core GEMM for a dense problem of M tokens.  Above 128 tokens the tile is 256
-// (FP8W8A16_PREFILL_BT=128 selects the 128-token tile with double-buffered accumulators instead).
-int dense_token_tile(int M) {
-    static int prefill_bt = -1;
-    if (prefill_bt < 0) {
-        const char* e = getenv("FP8W8A16_PREFILL_BT");
-        prefill_bt = (e && atoi(e) == 128) ? 128 : 256;
-    }
-    const int bt = tc_pick_bt(M);
-    return bt > 128 ? prefill_bt : bt;
-}
+// Token tile of the tensor-core GEMM for a dense problem of M tokens: the next of 16 / 32 / 64 / 128 at or above M, 256 beyond.
+int dense_token_tile(int M) { return tc_pick_bt(M); }
 
 // Largest token count served by the CUDA-core GEMV under ALGO_AUTO (the reference has the same kind of
 // knob, _COALESCED_GEMV_M_MAX, src/fp8_w8a16_sm70/vllm_serve.py:1063-1072).  Default 1: measured on B200 the
@@ -119,7 +112,8 @@ int check_common(const void* x, const void* w, const void* scales, const void* o
 }
 
 int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_dtype, __half* out, int M, int N, int K,
-              int block_h, void* workspace, size_t workspace_bytes, cudaStream_t st, const ArParams* ar = nullptr) {
+              int block_h, void* workspace, size_t workspace_bytes, cudaStream_t st, const ArParams* ar = nullptr,
+              const __half* residual = nullptr) {
     const int bt = dense_token_tile(M), bk = tc_block_k(bt, false);
     const int token_tiles = (M + bt - 1) / bt;
     const int64_t tiles = (int64_t)((N + 127) / 128) * token_tiles;
@@ -141,6 +135,7 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
     L.p.num_experts = 1;
     L.p.out = out;
     L.p.ldo = N;
+    L.p.residual = residual;
     L.p.n_token_tiles = token_tiles;
     // many tiles per CTA: whole tiles cost < 12 % in the last wave and need no partial-tile traffic
     L.p.no_split = (tiles > (int64_t)tc_max_tiles_with_tickets() || tiles >= 8ll * tc_grid(bt, false)) ? 1 : 0;
@@ -153,24 +148,6 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
     W8A16_REQUIRE(L.max_units < (1ll << 31), FP8W8A16_ERR_UNSUPPORTED, "linear: problem too large for 32-bit work indices");
     L.p.cluster_size = tc_cluster_size(tiles, (K + bk - 1) / bk, bt, false);
     L.cluster_tiles = tiles;
-    // Optional (library built with -DW8A16_HYBRID_STREAMK and FP8W8A16_HYBRID_STREAMK=1): stream-K with at least one tile per CTA (gate_up at decode sizes: 400 tiles on
-    // 296 CTAs) lets every CTA take whole tiles first, stored directly, and splits only the remainder.  Measured on B200
-    // it is a wash (gate_up +1 % at 2-8 tokens, -1..3 % at 32-64), so the plain even split stays the default.
-    static int hybrid = -1;
-    if (hybrid < 0) {
-        const char* e = getenv("FP8W8A16_HYBRID_STREAMK");
-        hybrid = (e && atoi(e) == 1) ? 1 : 0;
-#ifndef W8A16_HYBRID_STREAMK
-        hybrid = 0;
-#endif
-    }
-    const int64_t grid = tc_grid(bt, false);
-    if (hybrid && ar == nullptr && !L.p.no_split && L.p.cluster_size <= 1 && tiles >= grid) {
-        if (tiles % grid == 0)
-            L.p.no_split = 1;                     // the tiles divide evenly: nothing to split at all
-        else
-            L.p.whole_rounds = (int)(tiles / grid);
-    }
     if (ar != nullptr && ar->world > 1) {
         W8A16_REQUIRE(N % 4 == 0, FP8W8A16_ERR_UNSUPPORTED, "linear_allreduce: N must be a multiple of 4 (got %d)", N);
         W8A16_REQUIRE((int64_t)M * N <= ar->part_elems, FP8W8A16_ERR_UNSUPPORTED,
@@ -185,17 +162,12 @@ int linear_tc(const __half* x, const uint8_t* w, const void* scales, int scale_d
     return tc_launch(L, bt, false, st);
 }
 
+// Token tile of the grouped GEMMs: twice the average rows per expert, rounded up to a tile size (measured on B200: the
+// best choice at every batch; 16 / 32 cover decode), at most 128 because the paired gate/up kernel keeps two accumulators.
 int token_tile_for(int R, int E) {
-    static int forced = -1;   // FP8W8A16_MOE_BT=16|32|64|128 overrides the choice (tuning aid)
-    if (forced < 0) {
-        const char* e = getenv("FP8W8A16_MOE_BT");
-        const int v = e ? atoi(e) : 0;
-        forced = (v == 16 || v == 32 || v == 64 || v == 128) ? v : 0;
-    }
-    if (forced) return forced;
     const int avg = (R + E - 1) / E;
     int bt = tc_pick_bt(2 * avg);
-    if (bt > 128) bt = 128;  // the paired gate/up kernel keeps two accumulators in TMEM: 128 tokens at most
+    if (bt > 128) bt = 128;
     return bt;
 }
 
@@ -447,6 +419,30 @@ int fp8w8a16_linear(const uint16_t* x, const uint8_t* w, const void* scales, int
     return fail(FP8W8A16_ERR_INVALID, "linear: unknown algo %d", algo);
 }
 
+int fp8w8a16_linear_residual(const uint16_t* x, const uint8_t* w, const void* scales, int scale_dtype, const uint16_t* residual,
+                             uint16_t* out, int M, int N, int K, int block_h, int block_w, void* workspace, size_t workspace_bytes,
+                             void* stream) {
+    int rc = check_common(x, w, scales, out, M, N, K, block_h, block_w, scale_dtype);
+    if (rc) return rc;
+    if (M == 0 || N == 0) return 0;
+    W8A16_REQUIRE(residual != nullptr, FP8W8A16_ERR_INVALID, "linear_residual: null residual");
+    return linear_tc(reinterpret_cast<const __half*>(x), w, scales, scale_dtype, reinterpret_cast<__half*>(out), M, N, K, block_h,
+                     workspace, workspace_bytes, (cudaStream_t)stream, nullptr, reinterpret_cast<const __half*>(residual));
+}
+
+int fp8w8a16_add_rmsnorm(const uint16_t* x, const uint16_t* residual, const uint16_t* weight, float eps, uint16_t* out,
+                         uint16_t* residual_out, int M, int N, void* stream) {
+    W8A16_REQUIRE(M >= 0 && N >= 0, FP8W8A16_ERR_INVALID, "add_rmsnorm: negative dimension");
+    if (M == 0 || N == 0) return 0;
+    W8A16_REQUIRE(x && weight && out, FP8W8A16_ERR_INVALID, "add_rmsnorm: null pointer");
+    W8A16_REQUIRE(N % 8 == 0 && aligned16(x) && aligned16(weight) && aligned16(out) && aligned16(residual) && aligned16(residual_out),
+                  FP8W8A16_ERR_UNSUPPORTED, "add_rmsnorm: N must be a multiple of 8 and all pointers 16-byte aligned");
+    W8A16_REQUIRE(residual == nullptr || residual_out != nullptr, FP8W8A16_ERR_INVALID, "add_rmsnorm: residual given without residual_out");
+    return launch_add_rmsnorm(reinterpret_cast<const __half*>(x), reinterpret_cast<const __half*>(residual),
+                              reinterpret_cast<const __half*>(weight), eps, reinterpret_cast<__half*>(out),
+                              reinterpret_cast<__half*>(residual_out), M, N, (cudaStream_t)stream);
+}
+
 int fp8w8a16_moe_topk_softmax(const void* logits, int logits_dtype, int M, int E, int topk, int renormalize,
                               int32_t* topk_ids, float* topk_weights, void* stream) {
     W8A16_REQUIRE(M >= 0, FP8W8A16_ERR_INVALID, "moe_topk_softmax: negative M");
@@ -672,18 +668,26 @@ int fp8w8a16_comm_destroy(fp8w8a16_comm* comm) {
     return 0;
 }
 
-int fp8w8a16_linear_allreduce(fp8w8a16_comm* comm, const uint16_t* x, const uint8_t* w, const void* scales, int scale_dtype,
-                              uint16_t* out, int M, int N, int K, int block_h, int block_w, void* workspace,
-                              size_t workspace_bytes, void* stream) {
+int fp8w8a16_linear_allreduce_residual(fp8w8a16_comm* comm, const uint16_t* x, const uint8_t* w, const void* scales, int scale_dtype,
+                                       const uint16_t* residual, uint16_t* out, int M, int N, int K, int block_h, int block_w,
+                                       void* workspace, size_t workspace_bytes, void* stream) {
     W8A16_REQUIRE(comm != nullptr, FP8W8A16_ERR_INVALID, "linear_allreduce: null communicator");
     int rc = check_common(x, w, scales, out, M, N, K, block_h, block_w, scale_dtype);
     if (rc) return rc;
     if (M == 0 || N == 0) return 0;
+    W8A16_REQUIRE(residual == nullptr || aligned16(residual), FP8W8A16_ERR_INVALID, "linear_allreduce: residual must be 16-byte aligned");
     ArParams ar;
     rc = comm_params(&comm->c, &ar);
     if (rc) return rc;
     return linear_tc(reinterpret_cast<const __half*>(x), w, scales, scale_dtype, reinterpret_cast<__half*>(out), M, N, K,
-                     block_h, workspace, workspace_bytes, (cudaStream_t)stream, &ar);
+                     block_h, workspace, workspace_bytes, (cudaStream_t)stream, &ar, reinterpret_cast<const __half*>(residual));
+}
+
+int fp8w8a16_linear_allreduce(fp8w8a16_comm* comm, const uint16_t* x, const uint8_t* w, const void* scales, int scale_dtype,
+                              uint16_t* out, int M, int N, int K, int block_h, int block_w, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+    return fp8w8a16_linear_allreduce_residual(comm, x, w, scales, scale_dtype, nullptr, out, M, N, K, block_h, block_w, workspace,
+                                              workspace_bytes, stream);
 }
 
 // ---- expert-parallel MoE over peer memory ------------------------------------------------------------------------

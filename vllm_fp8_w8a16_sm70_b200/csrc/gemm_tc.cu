@@ -45,25 +45,16 @@ namespace w8a16 {
 
 __device__ int g_tc_status = 0;  // sticky error bits set by bounded waits (0 = healthy)
 
-#ifdef W8A16_TC_TRACE
-// Debug build only: per-K-block timestamps of the three roles of CTA 0 (globaltimer, ns).
-__device__ unsigned long long g_tc_trace[3][256][6];
-__device__ unsigned long long g_tc_cta[512][4];   // per CTA: entry, after set-up + dependency wait, main loop done, exit
-#define TC_TRACE(role, idx, slot) do { if (blockIdx.x == 0 && (idx) < 256) g_tc_trace[role][idx][slot] = globaltimer_ns_raw(); } while (0)
-__device__ __forceinline__ unsigned long long globaltimer_ns_raw() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-#else
-#define TC_TRACE(role, idx, slot) do { } while (0)
-#endif
 
 namespace {
 
 constexpr int kThreadsTc = 352;   // warp 0 TMA, warp 1 MMA, warps 2-9 dequant + epilogue, warp 10 second MMA issuer
 constexpr int kDequantThreads = 256;
+#ifdef W8A16_TIMEOUT_MS
+constexpr unsigned long long kTimeoutNs = (unsigned long long)(W8A16_TIMEOUT_MS) * 1000000ull;   // development builds
+#else
 constexpr unsigned long long kTimeoutNs = 2000000000ull;
+#endif
 
 // ---- PTX wrappers -----------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -108,15 +99,21 @@ __device__ __forceinline__ uint32_t mbar_try_wait_suspend(uint32_t bar, uint32_t
     return ok;
 }
 
-// Bounded wait.  Returns false when the CTA has been declared dead (by this or another thread).
+// Bounded wait.  Returns false when the CTA has been declared dead (by this or another thread).  `dead` points at
+// the CTA's flag words: [0] dead, [kReadyWord] "the kernel this launch depends on has finished".  Converting and MMA
+// warps start before that (see the dependency wait in the kernel): what they then wait for cannot happen until the
+// previous kernel is done, however long that takes, so the clock of the bound only runs once the flag is up.
+constexpr int kReadyWord = 3;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* dead, int code) {
     if (mbar_try_wait(bar, parity)) return true;
-    const unsigned long long t0 = globaltimer_ns();
+    unsigned long long t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait_suspend(bar, parity, 2000u)) {
         if ((++spins & 0x3Fu) == 0u) {
             if (*dead) return false;
-            if (globaltimer_ns() - t0 > kTimeoutNs) {
+            if (dead[kReadyWord] == 0) {
+                t0 = globaltimer_ns();
+            } else if (globaltimer_ns() - t0 > kTimeoutNs) {
                 *dead = 1;
                 atomicOr(&g_tc_status, code);
                 return false;
@@ -265,10 +262,19 @@ struct TcCfg {
     static constexpr int kRawBytes = 128 * BK * kWT;           // FP8 tile(s)
     static constexpr int kXBytes = BT * BK * 2;                // FP16 activation tile
     static constexpr int kACols = (BK / 2) * kWT;              // TMEM columns of one dequantised stage
-    // One thread can start a tcgen05.mma only every ~56 cycles, far longer than a narrow MMA runs, so
-    // for small token tiles TWO warps issue: each takes half of the 16-element K steps of every K block
-    // and accumulates into its own TMEM columns; the epilogue adds the two halves in fixed order.
+    // One thread needs ~60-70 ns per tcgen05 instruction it issues (measured in this kernel), far longer than a narrow
+    // MMA runs, and a K block costs an issuer its MMAs plus two commits and two barrier waits.  For small token tiles
+    // TWO warps issue, each into its own TMEM accumulator columns; the epilogue adds the accumulators that were written
+    // in the segment, in fixed order.  Stage-owner form (kAltBlocks): each issuer OWNS the operand stages of its parity
+    // (stage index & 1) and takes exactly the K blocks that land in them - half the blocks each, so half the commits
+    // and waits, and two blocks' MMA chains in flight at once.  Because a stage is consumed by one issuer only, an issuer
+    // can never mistake an older fill of a stage for the one it waits for (a stage is not refilled before its owner has
+    // released it), however far the two issuers drift apart.
+#ifdef W8A16_BT64_ONE_ISSUER
+    static constexpr int kIssuers = (BT * kWT <= 128 && BT <= 32) ? 2 : 1;
+#else
     static constexpr int kIssuers = (BT * kWT <= 128 && BT <= 64) ? 2 : 1;
+#endif
     static constexpr int kAccCols = BT * kWT * kIssuers;       // one accumulator buffer
     // Small token tiles are sized so that TWO CTAs share an SM (half of shared memory and of TMEM
     // each): one CTA's prologue / epilogue hides behind the other's main loop, 16 warps dequantise.
@@ -277,6 +283,11 @@ struct TcCfg {
     static constexpr int kAccBufs = (2 * kAccCols + 2 * kACols <= kTmemBudget) ? 2 : 1;
     static constexpr int kNAraw = (kTmemBudget - kAccBufs * kAccCols) / kACols;
     static constexpr int kNA = kNAraw > 4 ? 4 : kNAraw;        // dequantised-operand stages (TMEM)
+    // Two issuers share the work in one of two ways.  With three or more operand stages each issuer OWNS the stages of
+    // its parity and takes the K blocks that land in them (see below); with only two stages that would leave each issuer a
+    // single stage and stall the converting warps, so both issuers work on every K block, half of its K steps each
+    // (measured on B200: stage ownership is 2-4 % faster at 16 tokens, 4-5 % slower at 64).
+    static constexpr bool kAltBlocks = kIssuers == 2 && kNA >= 3;
     static constexpr int kUsedCols = kAccBufs * kAccCols + kNA * kACols;
     // K blocks of the NEXT segment that are converted before the previous segment's epilogue runs
     static constexpr int kDefer = kAccBufs == 2 ? kNA : 0;
@@ -284,17 +295,32 @@ struct TcCfg {
     // grouped mode keeps the route table's two offset arrays (up to 256 experts + 1 each) in shared memory
     static constexpr int kTabExperts = 256;
     static constexpr int kTabBytes = 2 * (kTabExperts + 1) * 4 + 8;
-    static constexpr int kBudget = (kCtasPerSm == 2 ? 112 : 225) * 1024 - 2048 - kTabBytes;  // dynamic shared memory we allow ourselves
+    // Dynamic shared memory we allow ourselves: an SM has 228 KiB, 1 KiB of which every resident CTA reserves, and one CTA may
+    // take 227 KiB at most; what the rings may use is that minus the alignment slack, the barriers and the small tables.
+    static constexpr int kLimit = (kCtasPerSm == 2 ? 113 : 226) * 1024;
+    static constexpr int kBudget = kLimit - 1024 - 64 - 512 - kTabBytes;
     static constexpr int kNSraw = kBudget / (kRawBytes + kXBytes);
     static constexpr int kNS = kNSraw > 8 ? 8 : kNSraw;        // TMA ring stages
     static constexpr int kNumBars = 4 * kNS + 2 * kNA + 2;
     static constexpr int kSmemBytes = 1024 + kNS * (kRawBytes + kXBytes) + kNumBars * 8 + 64 + kTabBytes;
     static_assert(kNS >= 2, "not enough shared memory for a 2-stage TMA ring");
+    static_assert(kNumBars * 8 <= 512 && kSmemBytes <= kLimit, "shared-memory budget");
     static_assert(kNA >= 2, "not enough TMEM for two dequantised stages");
     static_assert(kTmemCols * kCtasPerSm <= 512, "co-resident CTAs exceed TMEM");
     // cluster split-K parks the fp32 partial tile in the (by then idle) raw-tile ring
     static constexpr bool kClusterOk = kWT * BT * 128 * 4 <= kNS * kRawBytes;
 };
+
+// Which issuers (bit i = issuer i) own at least one of the `nkb` K blocks of a segment whose first block lands in operand
+// stage `st0` of a ring of NA stages (owner of a stage = its index & 1).
+template <int NA>
+__device__ __forceinline__ uint32_t owners_mask(int st0, int nkb) {
+    uint32_t m = 0;
+#pragma unroll
+    for (int j = 0; j < NA; ++j)
+        if (j < nkb) m |= 1u << (((st0 + j) % NA) & 1);
+    return m;
+}
 
 // ring position: stage index and the parity of the current pass over the ring
 struct Ring {
@@ -315,7 +341,10 @@ __device__ __forceinline__ float gelu_erf_f(float x) { return 0.5f * x * (1.f + 
 // mode), `n` the output feature.  Rounding points follow the reference's grouped path
 // (src/fp8_w8a16_sm70/vllm_serve.py:1953-1990): GEMM output -> FP16, SiLU on FP16, product FP16,
 // route weight as FP16.
-template <bool PAIRED>
+// Dense mode with a residual (the decoder's residual stream, added where the row-parallel projection's output is
+// produced): out = RN16(acc + residual) - fp32 sum, one rounding.  In the fused all-reduce build this function only
+// writes this rank's partial to the staging buffer; the residual is added after the cross-rank sum (ar_exchange).
+template <bool PAIRED, bool AR = false>
 __device__ __forceinline__ void store_out(const TcParams& p, __half* out, int row, int n, float g, float u) {
     __half r;
     if (PAIRED) {
@@ -324,6 +353,7 @@ __device__ __forceinline__ void store_out(const TcParams& p, __half* out, int ro
         const __half a16 = __float2half_rn(p.activation == 2 ? gelu_erf_f(gf) : silu_f(gf));
         r = __float2half_rn(__half2float(a16) * __half2float(u16));
     } else {
+        if (!AR && p.residual != nullptr) g += __half2float(p.residual[(int64_t)row * p.ldo + n]);
         r = __float2half_rn(g);
         if (p.row_weight != nullptr) {
             const __half w16 = __float2half_rn(p.row_weight[row]);
@@ -334,46 +364,92 @@ __device__ __forceinline__ void store_out(const TcParams& p, __half* out, int ro
 }
 
 // ---- work decomposition ------------------------------------------------------------------------------
-// The launch is persistent ("stream-K"): the work is the sequence of all (output tile, K block) units,
-// tile-major, and CTA c owns the contiguous unit range [c * U, (c + 1) * U).  A CTA therefore walks a
-// few SEGMENTS, each a run of K blocks of one output tile.  A tile whose K range is covered by one
-// CTA is stored directly; otherwise every contributor writes its fp32 partial tile to its own slot
-// of the workspace and the last one to arrive (ticket counter) adds the slots in ascending CTA order.
+// The launch is persistent.  The work is made of (output tile, K block) units; a CTA walks a few SEGMENTS, each a run
+// of K blocks of one output tile, in one of three schedules chosen on the host from the shape alone:
+//   cluster   one thread-block cluster per tile, rank in cluster = K range (synchronous split-K)
+//   tiles     whole tiles only, dealt round-robin: tile = cta + i * grid
+//   stream-K  all units, tile-major, are cut into `grid` balanced contiguous ranges (sizes differ by at most one unit).  A
+//             tile whose K range is covered by one CTA is stored directly; otherwise every contributor writes its fp32
+//             partial tile to its own slot of the workspace and the last one to arrive (ticket counter) adds the slots in
+//             ascending CTA order.
 struct Seg {
     int tile, slab, expert, row_begin, rows_valid, kb0, nkb;
     int first_c, n_contrib;
-    int tkey;   // the tile's index in the space the stream-K split is computed in (== tile unless whole tiles come first)
+    int tkey;   // stream-K: the tile's index (its ticket and the key of its partial slots); -1 otherwise
+    int a_stage0;   // operand-ring stage of the segment's first K block (set by the converting warps; see owners_mask)
 };
 
-template <int BT, bool HYBRID = true>
-__device__ __forceinline__ void get_seg(const TcParams& p, bool grouped, const int* tile_off, const int* exp_off, int u, int u_end,
-                                        int total_kb, int n_tt, int units_per_cta, Seg& s) {
-    const int v = u / total_kb;
-    s.kb0 = u - v * total_kb;
-    s.nkb = min(total_kb - s.kb0, u_end - u);
-    const int rounds = HYBRID ? p.whole_rounds : 0;   // (compiled out of the paired and the fused all-reduce builds)
-    if (p.no_split) {
-        // whole tiles, dealt round-robin: at any moment the CTAs work on gridDim.x consecutive tiles (token tiles
-        // fastest), so a weight slab is in flight for all its token tiles at once and is read from HBM once
-        const int per_cta = units_per_cta / total_kb;
-        const int c = v / per_cta;
-        s.tile = (v - c * per_cta) * (int)gridDim.x + c;
-        s.tkey = s.tile;
-    } else if (rounds > 0) {
-        // hybrid: the CTA's own coordinate space is [0, rounds) whole tiles, then its share of the remaining tiles
-        if (v < rounds) {
-            s.tile = (int)blockIdx.x + v * (int)gridDim.x;
-            s.tkey = -1;
-        } else {
-            s.tkey = v - rounds;
-            s.tile = rounds * (int)gridDim.x + s.tkey;
-        }
-    } else {
-        s.tile = v;
-        s.tkey = v;
+struct Sched {
+    int n_tt;
+    int q, r;                   // stream-K: total units = q * grid + r; the first r CTAs own q + 1 units, the others q
+    int u_begin, u_end;
+    // first unit of CTA c's range, and the CTA that owns unit u (32-bit arithmetic only)
+    __device__ __forceinline__ int begin_of(int c) const { return c * q + min(c, r); }
+    __device__ __forceinline__ int owner_of(int u) const {
+        const int big = r * (q + 1);
+        return u < big ? u / (q + 1) : r + (u - big) / q;    // (q >= 1 whenever the second branch is reached)
     }
-    s.slab = s.tile / n_tt;             // token tiles fastest: concurrently running CTAs share a weight slab
-    const int tt = s.tile - s.slab * n_tt;
+};
+
+__device__ __forceinline__ void make_sched(const TcParams& p, int total_kb, int n_tt, int n_slabs, Sched& sc) {
+    const int cta = blockIdx.x, G = gridDim.x;
+    const int total_tiles = n_tt * n_slabs;
+    sc.n_tt = n_tt;
+    sc.q = sc.r = 0;
+    if (p.cluster_size > 1) {
+        // synchronous split-K: cluster = tile, rank in cluster = K range (every rank gets at least one block)
+        const int S = p.cluster_size;
+        const int tile = cta / S, rnk = cta - tile * S;
+        const int per = (total_kb + S - 1) / S;
+        const int b = min(total_kb, rnk * per), e = min(total_kb, b + per);
+        sc.u_begin = tile < total_tiles ? tile * total_kb + b : 0;
+        sc.u_end = tile < total_tiles ? tile * total_kb + e : 0;
+    } else if (p.no_split) {
+        const int per_cta = (total_tiles + G - 1) / G;
+        const int mine = cta < total_tiles ? (total_tiles - cta + G - 1) / G : 0;
+        sc.u_begin = cta * per_cta * total_kb;
+        sc.u_end = sc.u_begin + mine * total_kb;
+    } else {
+        const int units = total_tiles * total_kb;
+        sc.q = units / G;
+        sc.r = units - sc.q * G;
+        sc.u_begin = sc.begin_of(cta);
+        sc.u_end = sc.begin_of(cta + 1);
+    }
+}
+
+template <int BT>
+__device__ __forceinline__ void get_seg(const TcParams& p, bool grouped, const int* tile_off, const int* exp_off, int u, int total_kb,
+                                        int n_slabs, const Sched& sc, Seg& s) {
+    s.first_c = 0;
+    s.n_contrib = 1;
+    s.tkey = -1;
+    s.a_stage0 = 0;
+    if (p.cluster_size > 1) {
+        const int v = u / total_kb;
+        s.kb0 = u - v * total_kb;
+        s.nkb = sc.u_end - u;
+        s.tile = v;
+    } else if (p.no_split) {
+        // whole tiles, dealt round-robin: at any moment the CTAs work on `grid` consecutive tiles (token tiles fastest),
+        // so a weight slab is in flight for all its token tiles at once and is read from HBM once
+        const int v = u / total_kb;
+        const int per_cta = (sc.n_tt * n_slabs + (int)gridDim.x - 1) / (int)gridDim.x;
+        const int c = v / per_cta;
+        s.kb0 = 0;
+        s.nkb = total_kb;
+        s.tile = (v - c * per_cta) * (int)gridDim.x + c;
+    } else {
+        const int v = u / total_kb;
+        s.kb0 = u - v * total_kb;
+        s.nkb = min(total_kb - s.kb0, sc.u_end - u);
+        s.tkey = v;
+        s.tile = v;
+        s.first_c = sc.owner_of(v * total_kb);
+        s.n_contrib = sc.owner_of((v + 1) * total_kb - 1) - s.first_c + 1;
+    }
+    s.slab = s.tile / sc.n_tt;             // token tiles fastest: concurrently running CTAs share a weight slab
+    const int tt = s.tile - s.slab * sc.n_tt;
     s.expert = 0;
     if (grouped) {
         int lo = 0, hi = p.num_experts;  // largest e with tile_offsets[e] <= tt
@@ -388,25 +464,18 @@ __device__ __forceinline__ void get_seg(const TcParams& p, bool grouped, const i
         s.row_begin = tt * BT;
         s.rows_valid = min(BT, p.M - s.row_begin);
     }
-    if (p.no_split || s.tkey < 0) {
-        s.first_c = 0;
-        s.n_contrib = 1;
-    } else {
-        s.first_c = (s.tkey * total_kb) / units_per_cta;
-        s.n_contrib = ((s.tkey + 1) * total_kb - 1) / units_per_cta - s.first_c + 1;
-    }
 }
 
-// Workspace slot of contributor `c` for `tile`: slot 0 if the tile is the first one the CTA touches,
-// slot 1 otherwise (a CTA has at most two partially covered tiles: its first and its last).
-__device__ __forceinline__ int partial_slot(int c, int tile, int total_kb, int units_per_cta) {
-    return ((c * units_per_cta) / total_kb == tile) ? 2 * c : 2 * c + 1;
+// Workspace slot of contributor `c` for tile `tkey`: slot 0 if the tile is the first one the CTA's range touches, slot 1
+// otherwise (a range has at most two partially covered tiles: its first and its last).
+__device__ __forceinline__ int partial_slot(int c, int tkey, int total_kb, const Sched& sc) {
+    return (sc.begin_of(c) / total_kb == tkey) ? 2 * c : 2 * c + 1;
 }
 
 // Exchange of one region of an output tile between the ranks (see ArParams).  `stage` holds this rank's FP16
 // values; every thread handles groups of four consecutive features.  Kept out of line: it runs once per tile and
 // must not cost the main loop registers.
-__device__ __noinline__ void ar_exchange(const ArParams& ar, const __half* stage, uint32_t epoch, int N, int64_t ldo,
+__device__ __noinline__ void ar_exchange(const ArParams& ar, const __half* stage, const __half* residual, uint32_t epoch, int N, int64_t ldo,
                                          int row_begin, int rows_valid, int n0, int lo, int hi, int td, volatile int* s_dead) {
     const int64_t box = (int64_t)(epoch & 1u) * ar.world;     // first source slot of this launch's parity
     const uint2* mine = ar.inbox[ar.rank];
@@ -469,6 +538,12 @@ __device__ __noinline__ void ar_exchange(const ArParams& ar, const __half* stage
             }
         }
         if (dead) break;
+        if (residual != nullptr) {     // the residual stream joins the cross-rank sum before the one rounding
+            const uint2 rv = *reinterpret_cast<const uint2*>(residual + off);
+            const float2 ra = __half22float2(*reinterpret_cast<const __half2*>(&rv.x));
+            const float2 rb = __half22float2(*reinterpret_cast<const __half2*>(&rv.y));
+            acc.x += ra.x; acc.y += ra.y; acc.z += rb.x; acc.w += rb.y;
+        }
         const __half2 o0 = __floats2half2_rn(acc.x, acc.y), o1 = __floats2half2_rn(acc.z, acc.w);
         uint2 o;
         o.x = *reinterpret_cast<const uint32_t*>(&o0);
@@ -485,19 +560,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     static_assert(!(AR && PAIRED), "the fused all-reduce is a dense (row-parallel) mode");
     using C = TcCfg<BT, BK, PAIRED>;
     constexpr int kNS = C::kNS, kNA = C::kNA;
-#ifdef W8A16_HYBRID_STREAMK
-    constexpr bool kHybrid = !PAIRED && !AR;   // whole tiles before the stream-K share: dense launches only
-#else
-    constexpr bool kHybrid = false;            // measured neutral on B200: left out of the default build (it costs registers)
-#endif
 
     // Programmatic dependent launch: let the next kernel of the stream start its own set-up as soon as
     // this grid's CTAs are resident; it will wait (griddepcontrol.wait) for this grid to finish before
     // it reads or writes global memory.
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-#ifdef W8A16_TC_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 512) g_tc_cta[blockIdx.x][0] = globaltimer_ns_raw();
-#endif
 
     // ---- shared memory carve-up (1024-byte aligned tiles) ----
     extern __shared__ uint8_t smem_dyn[];
@@ -513,36 +580,12 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     uint32_t* s_tmem = reinterpret_cast<uint32_t*>(gen_tail);
     volatile int* s_dead = reinterpret_cast<volatile int*>(gen_tail + 4);
     volatile int* s_ticket = reinterpret_cast<volatile int*>(gen_tail + 8);
+    volatile int* s_ready = s_dead + kReadyWord;          // set once the dependency wait has been passed (see mbar_wait)
     int* s_tab = reinterpret_cast<int*>(gen_tail + 64);   // [kTabExperts + 1] tile offsets, then [kTabExperts + 1] row offsets
     const int* tab_tile = p.tile_offsets;                 // route-table offsets: global, or their shared-memory copy
     const int* tab_exp = p.expert_offsets;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < kNS; ++i) {
-            mbar_init(bar_full_raw + 8 * i, 1);
-            mbar_init(bar_empty_raw + 8 * i, kDequantThreads);
-            mbar_init(bar_full_x + 8 * i, 1);
-            mbar_init(bar_empty_x + 8 * i, C::kIssuers);
-        }
-        for (int i = 0; i < kNA; ++i) {
-            mbar_init(bar_full_a + 8 * i, kDequantThreads);
-            mbar_init(bar_empty_a + 8 * i, C::kIssuers);
-        }
-        mbar_init(bar_acc, C::kIssuers);
-        mbar_init(bar_acc + 8, C::kIssuers);
-        *s_dead = 0;
-        s_ticket[0] = 0;
-        s_ticket[1] = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) tmem_alloc(smem_u32(s_tmem), C::kTmemCols);
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = *s_tmem;
-    const uint32_t tmem_a0 = tmem_base + C::kAccBufs * C::kAccCols;  // first column of the dequantised-operand stages
 
     // ---- this CTA's unit range ----
     // Dense problems know it from the launch parameters alone; grouped ones read the tile count from
@@ -551,76 +594,61 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
     const int total_kb = (p.K + BK - 1) / BK;
     const int n_slabs = (p.N + 127) / 128;
     const int cta = blockIdx.x;
-    int n_tt = p.n_token_tiles, total_units = 0, units_per_cta = 0, u_begin = 0, u_end = 0;
-    int jump_from = -1, jump_to = 0;
-    auto set_range = [&]() {
-        const int total_tiles = n_tt * n_slabs;
-        total_units = total_tiles * total_kb;
-        if (p.cluster_size > 1) {
-            // synchronous split-K: cluster = tile, rank in cluster = K range (every rank gets at least one block)
-            const int S = p.cluster_size;
-            const int tile = cta / S, rnk = cta - tile * S;
-            const int per = (total_kb + S - 1) / S;
-            units_per_cta = per;
-            const int b = min(total_kb, rnk * per), e = min(total_kb, b + per);
-            u_begin = tile < total_tiles ? tile * total_kb + b : 0;
-            u_end = tile < total_tiles ? tile * total_kb + e : 0;
-        } else if (p.no_split) {
-            // whole tiles only, tile = cta + i * gridDim.x (see get_seg); units index a per-CTA virtual range
-            units_per_cta = (total_tiles + (int)gridDim.x - 1) / (int)gridDim.x * total_kb;
-            const int mine = cta < total_tiles ? (total_tiles - cta + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-            u_begin = cta * units_per_cta;
-            u_end = u_begin + mine * total_kb;
-        } else if (kHybrid && p.whole_rounds > 0) {
-            // hybrid: whole tiles first (coordinates [0, lenA)), then this CTA's stream-K share [bB, eB) of the remaining
-            // tiles, placed at lenA + [bB, eB) so that tile boundaries stay at multiples of total_kb
-            const int lenA = p.whole_rounds * total_kb;
-            const int units_b = (total_tiles - p.whole_rounds * (int)gridDim.x) * total_kb;
-            units_per_cta = (units_b + (int)gridDim.x - 1) / (int)gridDim.x;
-            const int bB = min(units_b, cta * units_per_cta), eB = min(units_b, bB + units_per_cta);
-            u_begin = 0;
-            u_end = lenA + eB;
-            jump_from = lenA;
-            jump_to = lenA + bB;
-        } else {
-            units_per_cta = (total_units + (int)gridDim.x - 1) / (int)gridDim.x;
-            u_begin = cta * units_per_cta;
-            u_end = min(total_units, u_begin + units_per_cta);
-        }
-    };
-    // next coordinate after a segment of nkb blocks (the hybrid schedule skips from the whole tiles to the CTA's share)
-    auto advance = [&](int u, int nkb) -> int {
-        u += nkb;
-        return u == jump_from ? jump_to : u;
-    };
-    if (!grouped) set_range();
+    Sched sc;
+    sc.u_begin = sc.u_end = 0;
+    if (!grouped) make_sched(p, total_kb, p.n_token_tiles, n_slabs, sc);
 
-    // The weights are constants of the model, not results of the previous kernel: the producer requests
-    // the first ring of weight tiles BEFORE the dependency wait, so that under programmatic dependent
-    // launch the HBM latency of the first tiles hides behind the previous kernel's tail.
     int w_preissued = 0;
-    if (!grouped && warp == 0 && lane == 0) {
-        for (int u = u_begin; u < u_end && w_preissued < kNS;) {
-            Seg sg;
-            get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
-            const int w_row = sg.slab * 128;
-            for (int j = 0; j < sg.nkb && w_preissued < kNS; ++j, ++w_preissued) {
-                const int s = w_preissued;  // ring is empty: stage index == unit index, no wait needed
-                mbar_arrive_expect_tx(bar_full_raw + 8 * s, C::kRawBytes);
-                tma_load_2d(s_raw + s * C::kRawBytes, &map_w, bar_full_raw + 8 * s, (sg.kb0 + j) * BK, w_row);
-                if (PAIRED) tma_load_2d(s_raw + s * C::kRawBytes + 128 * BK, &map_w, bar_full_raw + 8 * s, (sg.kb0 + j) * BK, w_row + p.pair_offset);
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kNS; ++i) {
+            mbar_init(bar_full_raw + 8 * i, 1);
+            mbar_init(bar_empty_raw + 8 * i, kDequantThreads);
+            mbar_init(bar_full_x + 8 * i, 1);
+            mbar_init(bar_empty_x + 8 * i, C::kAltBlocks ? 1 : C::kIssuers);   // released by the issuer(s) that consumed the stage
+        }
+        for (int i = 0; i < kNA; ++i) {
+            mbar_init(bar_full_a + 8 * i, kDequantThreads);
+            mbar_init(bar_empty_a + 8 * i, C::kAltBlocks ? 1 : C::kIssuers);
+        }
+        mbar_init(bar_acc, C::kIssuers);
+        mbar_init(bar_acc + 8, C::kIssuers);
+        *s_dead = 0;
+        *s_ready = 0;
+        s_ticket[0] = 0;
+        s_ticket[1] = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // The weights are constants of the model, not results of the previous kernel: this thread (the TMA producer)
+        // requests the first ring of weight tiles right here - before the CTA-wide set-up barrier, before the tensor
+        // memory allocation and before the dependency wait - so that under programmatic dependent launch the HBM
+        // latency of the first tiles hides behind the previous kernel's tail and this kernel's own set-up.
+        if (!grouped) {
+            for (int u = sc.u_begin; u < sc.u_end && w_preissued < kNS;) {
+                Seg sg;
+                get_seg<BT>(p, grouped, tab_tile, tab_exp, u, total_kb, n_slabs, sc, sg);
+                const int w_row = sg.slab * 128;
+                for (int j = 0; j < sg.nkb && w_preissued < kNS; ++j, ++w_preissued) {
+                    const int st = w_preissued;  // ring is empty: stage index == unit index, no wait needed
+                    mbar_arrive_expect_tx(bar_full_raw + 8 * st, C::kRawBytes);
+                    tma_load_2d(s_raw + st * C::kRawBytes, &map_w, bar_full_raw + 8 * st, (sg.kb0 + j) * BK, w_row);
+                    if (PAIRED) tma_load_2d(s_raw + st * C::kRawBytes + 128 * BK, &map_w, bar_full_raw + 8 * st, (sg.kb0 + j) * BK, w_row + p.pair_offset);
+                }
+                u += sg.nkb;
             }
-            u = advance(u, sg.nkb);
         }
     }
-
+    if (warp == 1) tmem_alloc(smem_u32(s_tmem), C::kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+    const uint32_t tmem_a0 = tmem_base + C::kAccBufs * C::kAccCols;  // first column of the dequantised-operand stages
     // Likewise the scales of the first segment's first two K blocks (model constants): fetched by the converting warps
     // before the dependency wait, so that their L2 / HBM latency is not the first thing on the critical path after it.
     __half pre_cur[C::kWT], pre_nx1[C::kWT];
     bool pre_ok = false;
-    if (!grouped && warp >= 2 && warp <= 9 && u_begin < u_end) {
+    if (!grouped && warp >= 2 && warp <= 9 && sc.u_begin < sc.u_end) {
         Seg sg0;
-        get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, sg0);
+        get_seg<BT>(p, grouped, tab_tile, tab_exp, sc.u_begin, total_kb, n_slabs, sc, sg0);
         const int kb_last0 = sg0.kb0 + sg0.nkb - 1;
 #pragma unroll
         for (int wt = 0; wt < C::kWT; ++wt) {
@@ -633,13 +661,21 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         pre_ok = true;
     }
 
-    // Everything above read only launch parameters and model weights, so under programmatic dependent
-    // launch it may have overlapped the tail of the previous kernel in the stream.  From here on that
-    // kernel's results (activations, route tables, workspace) are needed.
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-#ifdef W8A16_TC_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 512) g_tc_cta[blockIdx.x][1] = globaltimer_ns_raw();
-#endif
+    // Everything above read only launch parameters and model weights, so under programmatic dependent launch it may
+    // have overlapped the tail of the previous kernel in the stream.  What still depends on that kernel's results:
+    //   the activation tiles (TMA producer), the output / partial-tile / ticket stores (epilogue), and - grouped launches
+    //   only - the route table, which fixes the schedule itself.
+    // A grouped launch therefore waits here with all its threads.  A dense launch does NOT: its TMA producer waits just
+    // before the first activation tile, its converting warps wait at the start of their first epilogue, and in between
+    // the weight tiles that were requested above are converted into the tensor-memory operand stages while the previous
+    // kernel is still finishing - when it is done, the MMAs only wait for the activation tiles.
+    auto dependency_wait = [&]() {
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+    };
+    if (grouped) {
+        dependency_wait();
+        if (threadIdx.x == 0) *s_ready = 1;
+    }
     if (grouped) {
         if (p.num_experts <= C::kTabExperts) {
             // every segment start searches these tables: keep them on chip
@@ -651,30 +687,30 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             tab_tile = s_tab;
             tab_exp = s_tab + C::kTabExperts + 1;
         }
-        n_tt = tab_tile[p.num_experts];
-        set_range();
+        make_sched(p, total_kb, tab_tile[p.num_experts], n_slabs, sc);
     }
-    const bool has_work = u_begin < u_end;  // uniform for the whole CTA
+    const int u_begin = sc.u_begin, u_end = sc.u_end;
+    const bool has_work = u_begin < u_end;  // uniform for the whole CTA (and, in cluster mode, for the whole cluster)
     // Fused all-reduce: this launch's epoch (one more than the count of finished fused launches; every rank makes
     // the same sequence of launches) tags the packets; the GEMM result itself is first left in a staging buffer.
-    unsigned int ar_epoch = 0;
-    __half* out_ptr = p.out;
-    if (AR) {
-        ar_epoch = *reinterpret_cast<volatile unsigned int*>(ar.ctrl) + 1u;
-        out_ptr = ar.part;
-    }
+    unsigned int ar_epoch = 0;     // read after the thread's own dependency wait (the previous fused launch closes it)
+    __half* out_ptr = AR ? ar.part : p.out;
 
     if (!has_work) {
         // nothing to do: fall through to the teardown (TMEM must still be returned)
     } else if (warp == 0) {
         // ================= TMA producer =================
         if (lane == 0) {
+            if (!grouped) {
+                dependency_wait();      // the activations are the previous kernel's output
+                *s_ready = 1;
+            }
             Ring ring;
             bool ok = true;
             int it = 0;   // K blocks handled so far; the first w_preissued of them already have their weight tile in flight
             for (int u = u_begin; u < u_end && ok;) {
                 Seg sg;
-                get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
+                get_seg<BT>(p, grouped, tab_tile, tab_exp, u, total_kb, n_slabs, sc, sg);
                 const int w_row = sg.expert * p.w_rows_per_expert + sg.slab * 128;
                 for (int j = 0; j < sg.nkb; ++j, ++it) {
                     const int s = ring.stage;
@@ -682,7 +718,6 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     if (it >= w_preissued) {
                         ok = mbar_wait(bar_empty_raw + 8 * s, ring.phase ^ 1u, s_dead, 1);
                         if (!ok) break;
-                        TC_TRACE(0, it, 0);
                         mbar_arrive_expect_tx(bar_full_raw + 8 * s, C::kRawBytes);
                         tma_load_2d(s_raw + s * C::kRawBytes, &map_w, bar_full_raw + 8 * s, k0, w_row);
                         if (PAIRED) tma_load_2d(s_raw + s * C::kRawBytes + 128 * BK, &map_w, bar_full_raw + 8 * s, k0, w_row + p.pair_offset);
@@ -695,7 +730,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         tma_load_2d(s_x + s * C::kXBytes + sl * (BT * 128), &map_x, bar_full_x + 8 * s, k0 + sl * 64, sg.row_begin);
                     ring.advance(kNS);
                 }
-                u = advance(u, sg.nkb);
+                u += sg.nkb;
             }
         }
     } else if (warp == 1 || warp == 10) {
@@ -708,42 +743,61 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             int si = 0;   // segment index: selects the accumulator buffer
             for (int u = u_begin; u < u_end && ok; ++si) {
                 const uint32_t d_acc = tmem_base + (uint32_t)((si % C::kAccBufs) * C::kAccCols + issuer * (BT * C::kWT));
-                const int tile = u / total_kb;
-                const int nkb = min(total_kb - (u - tile * total_kb), u_end - u);
+                // length of the segment that starts at u (as get_seg computes it, without the tile look-up)
+                int nkb;
+                if (p.cluster_size > 1) nkb = u_end - u;
+                else if (!p.no_split) nkb = min(total_kb - u % total_kb, u_end - u);
+                else nkb = total_kb;
+                const uint32_t owners = owners_mask<kNA>(ra.stage, nkb);
+                bool first = true;    // this issuer's first MMA of the segment overwrites its accumulator
                 for (int j = 0; j < nkb; ++j) {
-                    ok = mbar_wait(bar_full_a + 8 * ra.stage, ra.phase, s_dead, 4) &&
-                         mbar_wait(bar_full_x + 8 * rx.stage, rx.phase, s_dead, 8);
-                    if (!ok) break;
-                    if (issuer == 0) TC_TRACE(1, u - u_begin + j, 0);
-                    tc_fence_after();
-                    const uint32_t a_col = tmem_a0 + ra.stage * C::kACols;
-                    // one descriptor per K block; the 16-element K steps only add to its start-address field
-                    const uint64_t db0 = make_desc_sw128(s_x + rx.stage * C::kXBytes);
-                    constexpr int kSteps = C::kSlabs * 4;              // 16-element K steps per K block
-                    constexpr int kMine = kSteps / C::kIssuers;        // ... of which this issuer takes a contiguous half
+                    const bool mine = !C::kAltBlocks || C::kIssuers == 1 || (ra.stage & 1) == issuer;
+                    if (mine) {   // stage-owner scheme: only the K blocks in this issuer's operand stages
+                        ok = mbar_wait(bar_full_a + 8 * ra.stage, ra.phase, s_dead, 4) &&
+                             mbar_wait(bar_full_x + 8 * rx.stage, rx.phase, s_dead, 8);
+                        if (!ok) break;
+                        tc_fence_after();
+                        const uint32_t a_col = tmem_a0 + ra.stage * C::kACols;
+                        // one descriptor per K block; the 16-element K steps only add to its start-address field
+                        const uint64_t db0 = make_desc_sw128(s_x + rx.stage * C::kXBytes);
+                        constexpr int kSteps = C::kSlabs * 4;              // 16-element K steps per K block
+                        constexpr int kMine = C::kAltBlocks ? kSteps : kSteps / C::kIssuers;
+                        const int step0 = C::kAltBlocks ? 0 : issuer * kMine;
+                        const uint32_t first_acc = first ? 0u : 1u;
+                        first = false;
 #pragma unroll
-                    for (int t = 0; t < kMine; ++t) {
-                        const int step = issuer * kMine + t;
-                        const int sl = step >> 2, kk = step & 3;
-                        const uint64_t db = db0 + (uint64_t)((sl * (BT * 128) + kk * 32) >> 4);
-                        const uint32_t a_k = a_col + step * 8;             // 16 K elements = 8 columns
-                        if (t == 0) {
-                            const uint32_t acc = j > 0 ? 1u : 0u;              // first MMA of a segment overwrites
-                            umma_f16_ts(d_acc, a_k, db, idesc, acc);
-                            if (PAIRED) umma_f16_ts(d_acc + BT, a_k + BK / 2, db, idesc, acc);
-                        } else {
-                            umma_f16_ts_acc(d_acc, a_k, db, idesc);
-                            if (PAIRED) umma_f16_ts_acc(d_acc + BT, a_k + BK / 2, db, idesc);
+                        for (int t = 0; t < kMine; ++t) {
+                            const int step = step0 + t;
+                            const int sl = step >> 2, kk = step & 3;
+                            const uint64_t db = db0 + (uint64_t)((sl * (BT * 128) + kk * 32) >> 4);
+                            const uint32_t a_k = a_col + step * 8;             // 16 K elements = 8 columns
+                            if (t == 0) {
+                                umma_f16_ts(d_acc, a_k, db, idesc, first_acc);
+                                if (PAIRED) umma_f16_ts(d_acc + BT, a_k + BK / 2, db, idesc, first_acc);
+                            } else {
+                                umma_f16_ts_acc(d_acc, a_k, db, idesc);
+                                if (PAIRED) umma_f16_ts_acc(d_acc + BT, a_k + BK / 2, db, idesc);
+                            }
                         }
+                        umma_commit(bar_empty_a + 8 * ra.stage);
+                        umma_commit(bar_empty_x + 8 * rx.stage);
                     }
-                    umma_commit(bar_empty_a + 8 * ra.stage);
-                    umma_commit(bar_empty_x + 8 * rx.stage);
-                    if (issuer == 0) TC_TRACE(1, u - u_begin + j, 1);
                     ra.advance(kNA);
                     rx.advance(kNS);
                 }
-                if (ok) umma_commit(bar_acc + 8 * (si % C::kAccBufs));  // accumulators of this segment are complete
-                u = advance(u, nkb);
+                // The accumulators of this segment are complete when every issuer's MMAs are: the barrier takes one arrival
+                // per issuer.  An issuer that owns no block of a short segment does not arrive at all (nothing orders it
+                // behind the pipeline; a free-running arrival could complete a later phase of the barrier early): the
+                // issuer that does own blocks arrives twice instead.
+                if (ok) {
+                    if (!C::kAltBlocks || C::kIssuers == 1) {
+                        umma_commit(bar_acc + 8 * (si % C::kAccBufs));
+                    } else if (owners & (1u << issuer)) {
+                        umma_commit(bar_acc + 8 * (si % C::kAccBufs));
+                        if (owners == (1u << issuer)) umma_commit(bar_acc + 8 * (si % C::kAccBufs));
+                    }
+                }
+                u += nkb;
             }
         }
     } else if (warp >= 2 && warp <= 9) {
@@ -763,8 +817,6 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         constexpr int kTileFloats = C::kWT * BT * 128;
 
         Ring rr, ra;   // raw-tile ring (shared memory) and dequantised-operand ring (TMEM)
-        int tr_i = 0;  // K blocks converted so far (index of the debug trace; unused otherwise)
-        (void)tr_i;
         bool ok = true;
 
         // Fused all-reduce of one finished region of an output tile (16-byte groups [lo, hi) of the BT x 128 tile).
@@ -778,7 +830,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             epi_bar_sync();
             int dead = dead_in | *s_dead;
             const int n0 = sg.slab * 128;
-            if (!dead) ar_exchange(ar, out_ptr, ar_epoch, p.N, p.ldo, sg.row_begin, sg.rows_valid, n0, lo, hi, td, s_dead);
+            if (!dead) ar_exchange(ar, out_ptr, p.residual, ar_epoch, p.N, p.ldo, sg.row_begin, sg.rows_valid, n0, lo, hi, td, s_dead);
             // one verdict for the whole CTA, published by one thread between two barriers taken by all
             epi_bar_sync();
             if (td == 0) s_ticket[1] = *s_dead;
@@ -791,11 +843,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         // thread 0 publishes; every one of the 256 threads calls it once per segment and takes both
         // barriers inside, whatever its own `ok` says, so a timed-out wait can never strand the others.
         auto epilogue = [&](const Seg& sg, int si) -> int {
+            if (!grouped) dependency_wait();   // (returns at once after the first time) output, partial tiles and tickets may be in use until now
+            if (AR) ar_epoch = *reinterpret_cast<volatile unsigned int*>(ar.ctrl) + 1u;
             const int n0 = sg.slab * 128;
             const uint32_t t_acc = t_lane + (uint32_t)((si % C::kAccBufs) * C::kAccCols);
-            if (td == 0) TC_TRACE(0, 200, 0);
             if (ok) ok = mbar_wait(bar_acc + 8 * (si % C::kAccBufs), (uint32_t)(si / C::kAccBufs) & 1u, s_dead, 64);
-            if (td == 0) TC_TRACE(0, 200, 1);
             ok = __all_sync(0xFFFFFFFFu, ok) != 0;  // tcgen05.ld is warp-collective: keep the warp together
             const bool clustered = p.cluster_size > 1;
             const bool direct = !clustered && (sg.n_contrib == 1);
@@ -804,14 +856,21 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 const int n = n0 + n_local;
                 // partial tile: a workspace slot (stream-K), or this CTA's idle raw-tile ring (cluster split-K)
                 float* part = clustered ? reinterpret_cast<float*>(smem_dyn + (s_raw - dyn_base))
-                                        : p.partial + (int64_t)partial_slot(cta, sg.tkey, total_kb, units_per_cta) * kTileFloats;
+                                        : p.partial + (int64_t)partial_slot(cta, sg.tkey, total_kb, sc) * kTileFloats;
 #pragma unroll 1
                 for (int c0 = 0; c0 < kColsPerWarp; c0 += 8) {
                     const int col = hk * kColsPerWarp + c0;
                     float g[8], uu[8];
-                    tmem_ld8(t_acc + col, g);
-                    if (PAIRED) tmem_ld8(t_acc + BT + col, uu);
-                    if (C::kIssuers == 2) {   // second issuer's half of the K steps, added in fixed order
+                    // which issuers' accumulators hold this segment (both, in the scheme where both work on every block)
+                    const uint32_t owners = (C::kIssuers == 2 && C::kAltBlocks) ? owners_mask<kNA>(sg.a_stage0, sg.nkb) : (C::kIssuers == 2 ? 3u : 1u);
+                    if (owners & 1u) {
+                        tmem_ld8(t_acc + col, g);
+                        if (PAIRED) tmem_ld8(t_acc + BT + col, uu);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) g[j] = uu[j] = 0.f;
+                    }
+                    if (owners & 2u) {   // the second issuer's share, added in fixed order
                         float g2[8], u2[8];
                         tmem_ld8(t_acc + BT * C::kWT + col, g2);
                         if (PAIRED) tmem_ld8(t_acc + BT * C::kWT + BT + col, u2);
@@ -825,7 +884,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
 #pragma unroll
                         for (int j = 0; j < 8; ++j)
                             if (col + j < sg.rows_valid && n < p.N)
-                                store_out<PAIRED>(p, out_ptr, sg.row_begin + col + j, n, g[j], PAIRED ? uu[j] : 0.f);
+                                store_out<PAIRED, AR>(p, out_ptr, sg.row_begin + col + j, n, g[j], PAIRED ? uu[j] : 0.f);
                     } else if (clustered) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
@@ -841,7 +900,6 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     }
                 }
             }
-            if (td == 0) TC_TRACE(0, 200, 2);
             tc_fence_before();
             // Hand-off.  All 256 threads take both barriers in every segment, whatever happened above,
             // and act only on values that thread 0 publishes between them, so that a timed-out wait
@@ -879,7 +937,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         for (int t = 0; t < 8; ++t) {
                             const int cc = sg.first_c + min(c0 + t, sg.n_contrib - 1);   // clamped: extra loads are ignored below
                             const float4* ps = reinterpret_cast<const float4*>(
-                                p.partial + (int64_t)partial_slot(cc, sg.tkey, total_kb, units_per_cta) * kTileFloats);
+                                p.partial + (int64_t)partial_slot(cc, sg.tkey, total_kb, sc) * kTileFloats);
                             a[t] = __ldcg(&ps[idx4]);
                             if (PAIRED) b[t] = __ldcg(&ps[BT * 32 + idx4]);
                         }
@@ -892,10 +950,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         }
                     }
                     const int row = sg.row_begin + ml, n = n0 + nl;
-                    store_out<PAIRED>(p, out_ptr, row, n, g.x, uu.x);
-                    if (n + 1 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 1, g.y, uu.y);
-                    if (n + 2 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 2, g.z, uu.z);
-                    if (n + 3 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 3, g.w, uu.w);
+                    store_out<PAIRED, AR>(p, out_ptr, row, n, g.x, uu.x);
+                    if (n + 1 < p.N) store_out<PAIRED, AR>(p, out_ptr, row, n + 1, g.y, uu.y);
+                    if (n + 2 < p.N) store_out<PAIRED, AR>(p, out_ptr, row, n + 2, g.z, uu.z);
+                    if (n + 3 < p.N) store_out<PAIRED, AR>(p, out_ptr, row, n + 3, g.w, uu.w);
                 }
                 if (td == 0) p.tickets[sg.tile] = 0u;  // leave the counter clean for the next launch
                 if (AR) return ar_finish(sg, 0, BT * 32, dead_now);
@@ -910,8 +968,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         int stop = 0;
         for (int u = u_begin; u < u_end; ++si) {
             Seg sg;
-            get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, sg);
-            u = advance(u, sg.nkb);
+            get_seg<BT>(p, grouped, tab_tile, tab_exp, u, total_kb, n_slabs, sc, sg);
+            sg.a_stage0 = ra.stage;
+            u += sg.nkb;
             const int n0 = sg.slab * 128;
             // scale-grid rows for this thread's weight row(s); clamped so tail rows stay in bounds
             int64_t srow[C::kWT];
@@ -940,7 +999,7 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                 // the first scales of the NEXT segment travel while this one is converted: with short segments (a few
                 // K blocks per tile, as in the MoE down projection) their latency would otherwise open every tile
                 Seg nx;
-                get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u, u_end, total_kb, n_tt, units_per_cta, nx);
+                get_seg<BT>(p, grouped, tab_tile, tab_exp, u, total_kb, n_slabs, sc, nx);
                 const int kb_last_n = nx.kb0 + nx.nkb - 1;
 #pragma unroll
                 for (int wt = 0; wt < C::kWT; ++wt) {
@@ -963,12 +1022,9 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                     s_cur[wt] = s_nx1[wt];
                     s_nx1[wt] = s_nx2[wt];
                 }
-                if (td == 0) TC_TRACE(2, tr_i, 0);
                 ok = mbar_wait(bar_full_raw + 8 * s, rr.phase, s_dead, 16);
-                if (td == 0) TC_TRACE(2, tr_i, 1);
                 ok = ok && mbar_wait(bar_empty_a + 8 * sa, ra.phase ^ 1u, s_dead, 32);
                 if (!ok) break;
-                if (td == 0) TC_TRACE(2, tr_i, 2);
                 tc_fence_after();   // the MMAs that last read this TMEM stage are complete (empty_a): order our stores after them
 #pragma unroll
                 for (int wt = 0; wt < C::kWT; ++wt) {
@@ -987,14 +1043,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         tmem_st8(a_dst + chunk * 8, hw);   // 16 K elements = 8 columns
                     }
                 }
-                if (td == 0) TC_TRACE(2, tr_i, 3);
                 tmem_wait_st();
-                if (td == 0) TC_TRACE(2, tr_i, 4);
                 tc_fence_before();
                 mbar_arrive(bar_full_a + 8 * sa);
                 mbar_arrive(bar_empty_raw + 8 * s);
-                if (td == 0) TC_TRACE(2, tr_i, 5);
-                ++tr_i;
                 rr.advance(kNS);
                 ra.advance(kNA);
                 if (C::kDefer > 0 && pend_i >= 0 && j + 1 == min(C::kDefer, sg.nkb)) {
@@ -1023,12 +1075,10 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         if (!stop && pend_i >= 0) stop = epilogue(pend, pend_i);
         if (p.cluster_size > 1) {
             // every CTA of the cluster has parked its fp32 partial tile in its own shared memory
-            if (td == 0) TC_TRACE(0, 200, 3);
             cluster_sync_all();
-            if (td == 0) TC_TRACE(0, 200, 4);
             if (!stop) {
                 Seg last_sg;   // the one segment of this CTA
-                get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
+                get_seg<BT>(p, grouped, tab_tile, tab_exp, u_begin, total_kb, n_slabs, sc, last_sg);
                 const int S = p.cluster_size;
                 uint32_t rnk;
                 asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rnk));
@@ -1059,20 +1109,18 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
                         if (wt == 0) g = acc; else uu = acc;
                     }
                     const int row = last_sg.row_begin + ml, n = n0 + nl;
-                    store_out<PAIRED>(p, out_ptr, row, n, g.x, uu.x);
-                    if (n + 1 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 1, g.y, uu.y);
-                    if (n + 2 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 2, g.z, uu.z);
-                    if (n + 3 < p.N) store_out<PAIRED>(p, out_ptr, row, n + 3, g.w, uu.w);
+                    store_out<PAIRED, AR>(p, out_ptr, row, n, g.x, uu.x);
+                    if (n + 1 < p.N) store_out<PAIRED, AR>(p, out_ptr, row, n + 1, g.y, uu.y);
+                    if (n + 2 < p.N) store_out<PAIRED, AR>(p, out_ptr, row, n + 2, g.z, uu.z);
+                    if (n + 3 < p.N) store_out<PAIRED, AR>(p, out_ptr, row, n + 3, g.w, uu.w);
                 }
             }
-            if (td == 0) TC_TRACE(0, 200, 5);
             // this CTA has read what it needs from its peers; nobody may leave (and free its shared memory) before
             // every peer has said the same - the matching wait is taken in the teardown
             cluster_arrive();
-            if (td == 0) TC_TRACE(0, 201, 0);
             if (AR) {
                 Seg last_sg;
-                get_seg<BT, kHybrid>(p, grouped, tab_tile, tab_exp, u_begin, u_end, total_kb, n_tt, units_per_cta, last_sg);
+                get_seg<BT>(p, grouped, tab_tile, tab_exp, u_begin, total_kb, n_slabs, sc, last_sg);
                 uint32_t rnk;
                 asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rnk));
                 const int chunk = (BT * 32 + p.cluster_size - 1) / p.cluster_size;
@@ -1082,15 +1130,11 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         }
     }
 
-#ifdef W8A16_TC_TRACE
-    if (threadIdx.x == 64 && blockIdx.x < 512) g_tc_cta[blockIdx.x][2] = globaltimer_ns_raw();
-#endif
     if (p.cluster_size > 1) {
         if (!(has_work && warp >= 2 && warp <= 9)) {
             cluster_sync_all();   // the dequant warps of a working CTA take the first barrier and the second arrive in their branch
             cluster_arrive();
         }
-        cluster_wait();
     }
     // ---- teardown: every thread arrives here, also after a timed-out wait ----
     if (*s_dead) {
@@ -1104,8 +1148,13 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
         tc_fence_after();
         tmem_dealloc(tmem_base, C::kTmemCols);
     }
+    // cluster split-K: nobody may leave (and free the shared memory its peers read their slices from) before every peer
+    // has said it is done reading; taken last, so that the wait overlaps the tensor-memory release above
+    if (p.cluster_size > 1) cluster_wait();
     if (AR && threadIdx.x == 0) {
         // the last CTA of the grid to get here closes the launch: the epoch every CTA read above is now finished
+        dependency_wait();     // (a CTA without work has not waited yet)
+        ar_epoch = *reinterpret_cast<volatile unsigned int*>(ar.ctrl) + 1u;
         __threadfence();
         const unsigned int prev = atomicAdd(&ar.ctrl[1], 1u);
         if (prev == gridDim.x - 1) {
@@ -1114,9 +1163,6 @@ k_gemm_tc(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUt
             *reinterpret_cast<volatile unsigned int*>(ar.ctrl) = ar_epoch;
         }
     }
-#ifdef W8A16_TC_TRACE
-    if (threadIdx.x == 0 && blockIdx.x < 512) g_tc_cta[blockIdx.x][3] = globaltimer_ns_raw();
-#endif
 }
 
 // ---- host side -----------------------------------------------------------------------------------
@@ -1309,15 +1355,7 @@ int max_active_clusters_for(int bt, bool paired, int cs) {
 
 }  // namespace
 
-int tc_block_k(int bt, bool paired) {
-    static int prefill_bk = -1;   // experiment knob: FP8W8A16_PREFILL_BK=128 uses 128-element K blocks for the 256-token tile
-    if (prefill_bk < 0) {
-        const char* e = getenv("FP8W8A16_PREFILL_BK");
-        prefill_bk = (e && atoi(e) == 128) ? 128 : 64;
-    }
-    if (!paired && bt == 256) return prefill_bk;
-    return (!paired && bt <= 64) ? 128 : 64;
-}
+int tc_block_k(int bt, bool paired) { return (!paired && bt <= 64) ? 128 : 64; }
 
 int tc_ctas_per_sm(int bt, bool paired) { return (bt * (paired ? 2 : 1) <= 64) ? 2 : 1; }
 
@@ -1335,15 +1373,8 @@ size_t tc_max_tiles_with_tickets() { return kTicketBytes / sizeof(unsigned int);
 // Only sizes whose clusters are ALL resident at once are considered (the occupancy query accounts for how
 // clusters pack into the GPCs): a second wave of clusters costs far more than the fix-up it replaces.
 int tc_cluster_size(int64_t tiles, int total_kb, int bt, bool paired) {
-    // FP8W8A16_CLUSTER_SPLITK: 0 = off, n >= 2 = largest cluster a tile's K range may be split over (default 8)
-    static int max_s = -1;
-    if (max_s < 0) {
-        const char* e = getenv("FP8W8A16_CLUSTER_SPLITK");
-        max_s = e ? atoi(e) : 8;
-        if (max_s > 8) max_s = 8;
-        if (max_s < 2) max_s = 0;
-    }
-    if (!max_s || tiles <= 0 || bt > 64) return 0;
+    const int max_s = 8;    // portable cluster size limit
+    if (tiles <= 0 || bt > 64) return 0;
     const int64_t capacity = tc_grid(bt, paired);
     int64_t s = capacity / tiles;
     if (s > max_s) s = max_s;
@@ -1384,9 +1415,7 @@ int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st) {
             case 32: W8A16_TC_CASE(32, 128, false);
             case 64: W8A16_TC_CASE(64, 128, false);
             case 128: W8A16_TC_CASE(128, 64, false);
-            case 256:
-                if (tc_block_k(256, false) == 128) W8A16_TC_CASE(256, 128, false);
-                W8A16_TC_CASE(256, 64, false);
+            case 256: W8A16_TC_CASE(256, 64, false);
         }
     } else {
         switch (bt) {
@@ -1401,14 +1430,6 @@ int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st) {
     return fail(FP8W8A16_ERR_UNSUPPORTED, "gemm_tc: unsupported token tile %d", bt);
 }
 
-#ifdef W8A16_TC_TRACE
-extern "C" int w8a16_debug_read_trace(unsigned long long* host, size_t bytes) {
-    return (int)cudaMemcpyFromSymbol(host, g_tc_trace, bytes);
-}
-extern "C" int w8a16_debug_read_cta(unsigned long long* host, size_t bytes) {
-    return (int)cudaMemcpyFromSymbol(host, g_tc_cta, bytes);
-}
-#endif
 
 int tc_read_status(int* out, int reset) {
     int v = 0;

@@ -28,12 +28,11 @@ struct TcParams {
     __half* out;                 // out[row * ldo + n]
     int64_t ldo;
     const float* row_weight;     // optional per-row multiplier (route weight), applied as FP16
+    const __half* residual;      // optional (dense): FP16 [M, ldo] added to the fp32 result before the one rounding
     int activation;              // paired mode: 1 = SiLU(gate) * up, 2 = GELU(gate) * up (erf form)
     // persistent stream-K work split
     int n_token_tiles;           // dense: ceil(M / BT); grouped: read from tile_offsets[E] on the device
     int no_split;                // 1: every CTA takes whole tiles only (no partial tiles, no tickets)
-    int whole_rounds;            // > 0 (dense stream-K with at least one tile per CTA): every CTA first takes this many
-                                 //      WHOLE tiles (tile = cta + i * grid), only the remaining tiles are split stream-K
     int cluster_size;            // > 1: synchronous split-K — the CTAs of a thread-block cluster share one output tile,
                                  //      each takes a K range, and they reduce through distributed shared memory
     float* partial;              // fp32 scratch: [gridDim.x][2][(1|2)][BT][128]

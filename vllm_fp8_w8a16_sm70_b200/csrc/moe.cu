@@ -160,6 +160,74 @@ __global__ void __launch_bounds__(256) k_router_topk(const __half* __restrict__ 
     }
 }
 
+// The same router for decode batches, spread over a thread-block cluster per token: with one CTA per token a single SM
+// would read the whole gate matrix (1 MiB at 128 experts x 4096: ~50 us); here every CTA of the cluster computes a
+// share of the experts and stores its logits straight into the shared memory of the cluster's first CTA (distributed
+// shared memory), which then selects.  Same arithmetic per logit, same selection code: identical results.
+constexpr int kRouterCluster = 8;
+
+template <typename W, int PER_LANE>
+__global__ void __launch_bounds__(256) k_router_topk_cluster(const __half* __restrict__ x, const W* __restrict__ gate, int M, int E, int H,
+                                                             int topk, int renorm, int shared_id, float routed_scale,
+                                                             int* __restrict__ ids, float* __restrict__ weights,
+                                                             float* __restrict__ logits_out) {
+    extern __shared__ __align__(16) unsigned char smem_router[];
+    __half* sx = reinterpret_cast<__half*>(smem_router);                         // [H]
+    float* sl = reinterpret_cast<float*>(smem_router + (size_t)H * sizeof(__half));  // [E] (used in the cluster's first CTA)
+    pdl_trigger();
+    pdl_wait();
+    uint32_t rank, nranks;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(nranks));
+    const int m = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int i = threadIdx.x * 8; i < H; i += 256 * 8)
+        *reinterpret_cast<uint4*>(sx + i) = *reinterpret_cast<const uint4*>(x + (int64_t)m * H + i);
+    __syncthreads();
+    uint32_t sl0;   // the first CTA's logit array, as a cluster-wide shared-memory address
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(sl0) : "r"((uint32_t)__cvta_generic_to_shared(sl)), "r"(0u));
+    for (int e = (int)rank * 8 + warp; e < E; e += 8 * (int)nranks) {
+        const W* wr = gate + (int64_t)e * H;
+        float acc = 0.f;
+        for (int i = lane * 8; i < H; i += 32 * 8) {
+            float wv[8];
+            if (sizeof(W) == 2) {
+                const uint4 q = *reinterpret_cast<const uint4*>(wr + i);
+                const W* h8 = reinterpret_cast<const W*>(&q);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) wv[j] = to_f32<W>(h8[j]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) wv[j] = to_f32<W>(wr[i + j]);
+            }
+            const uint4 xq = *reinterpret_cast<const uint4*>(sx + i);
+            const __half* x8 = reinterpret_cast<const __half*>(&xq);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc = fmaf(__half2float(x8[j]), wv[j], acc);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0) {
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(sl0 + (uint32_t)e * 4u), "f"(acc) : "memory");
+            if (logits_out != nullptr) logits_out[(int64_t)m * E + e] = acc;
+        }
+    }
+    // every CTA's logits are in the first CTA's shared memory once the whole cluster has passed this barrier
+    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
+    if (rank == 0 && warp == 0) {
+        const int ld = topk + (shared_id >= 0 ? 1 : 0);
+        int* my_ids = ids + (int64_t)m * ld;
+        float* my_w = weights + (int64_t)m * ld;
+        topk_row<float, PER_LANE>(sl, E, topk, renorm, my_ids, my_w, lane);
+        __syncwarp();
+        if (routed_scale != 1.0f)
+            for (int t = lane; t < topk; t += 32) my_w[t] *= routed_scale;
+        if (shared_id >= 0 && lane == 0) {
+            my_ids[topk] = shared_id;
+            my_w[topk] = 1.0f;
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------------
 // align: one CTA.  Stable counting sort of the routed rows by local expert id.
 // ------------------------------------------------------------------------------------------------
@@ -399,13 +467,38 @@ int launch_topk_softmax(const void* logits, int logits_dtype, int M, int E, int 
 }
 
 namespace {
+template <typename W, int PL>
+cudaError_t launch_router_cluster(const __half* x, const W* gate, int M, int E, int H, int topk, int renorm, int shared_id,
+                                  float routed_scale, int* ids, float* weights, float* logits_out, size_t smem, cudaStream_t st) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kRouterCluster, (unsigned)M);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;
+    attr[1].val.clusterDim.x = kRouterCluster;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 2;
+    return cudaLaunchKernelEx(&cfg, k_router_topk_cluster<W, PL>, x, gate, M, E, H, topk, renorm, shared_id, routed_scale, ids, weights, logits_out);
+}
+
 template <typename W>
 int launch_router_t(const __half* x, const W* gate, int M, int E, int H, int topk, int renorm, int shared_id, float routed_scale,
                     int* ids, float* weights, float* logits_out, cudaStream_t st) {
     const int per_lane = (E + 31) / 32;
     const size_t smem = (size_t)H * sizeof(__half) + (size_t)E * sizeof(float);
     cudaError_t le = cudaSuccess;
-#define W8A16_ROUTER(PL) le = launch_pdl(k_router_topk<W, PL>, dim3((unsigned)M), dim3(256), smem, st, x, gate, M, E, H, topk, renorm, shared_id, routed_scale, ids, weights, logits_out)
+    // Decode batches (few tokens, enough experts to share out): a cluster of CTAs per token.  Large batches already fill the
+    // machine with one CTA per token.  65535 bounds the y dimension of a grid.
+    const bool clustered = E >= 8 * kRouterCluster && M <= 512 && M <= 65535 && smem <= 48 * 1024;
+#define W8A16_ROUTER(PL)                                                                                                                   \
+    le = clustered ? launch_router_cluster<W, PL>(x, gate, M, E, H, topk, renorm, shared_id, routed_scale, ids, weights, logits_out, smem, st) \
+                   : launch_pdl(k_router_topk<W, PL>, dim3((unsigned)M), dim3(256), smem, st, x, gate, M, E, H, topk, renorm, shared_id, routed_scale, ids, weights, logits_out)
     if (per_lane <= 1) W8A16_ROUTER(1);
     else if (per_lane <= 2) W8A16_ROUTER(2);
     else if (per_lane <= 4) W8A16_ROUTER(4);

@@ -166,12 +166,22 @@ def fp8_e4m3_to_fp16_block_scaled(w: torch.Tensor, scales: torch.Tensor, N: int,
 # ------------------------------------------------------------------------------------------------
 # dense W8A16 linear
 # ------------------------------------------------------------------------------------------------
+def _check_residual(residual: Optional[torch.Tensor], M: int, N: int, dev) -> None:
+    if residual is None:
+        return
+    if residual.dtype != torch.float16 or tuple(residual.shape) != (M, N) or not residual.is_contiguous() or residual.device != dev:
+        raise RuntimeError(f"residual must be a contiguous float16 [{M}, {N}] tensor on {dev}")
+
+
 def w8a16_linear(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, N: int, K: int, block_h: int = 128,
-                 block_w: int = 128, algo: int = ALGO_AUTO, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                 block_w: int = 128, algo: int = ALGO_AUTO, out: Optional[torch.Tensor] = None,
+                 residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """x float16 [M, K] @ dequant(w [N, K], scales)^T -> float16 [M, N].
 
     One op for the reference's dense family (gemv_coalesced, gemv_coalesced_m, gemm_a1/a2/a3,
-    gemm_wmma_poc) and the dispatch among them (src/fp8_w8a16_sm70/vllm_serve.py:1032-1100)."""
+    gemm_wmma_poc) and the dispatch among them (src/fp8_w8a16_sm70/vllm_serve.py:1032-1100).
+    ``residual`` (float16 [M, N]): added to the fp32 result in the GEMM's epilogue before the one rounding
+    (tensor-core path at every M); ``out`` may be the same tensor."""
     w = _as_u8(w)
     dev = _require_cuda(x, w, scales)
     if x.dtype != torch.float16:
@@ -193,11 +203,37 @@ def w8a16_linear(x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, N: int,
         if need is None:
             need = _LINEAR_WS_BYTES[(M, N, K)] = lib.fp8w8a16_linear_workspace_bytes(M, N, K)
         ws = workspace(dev, need, st)
-        rc = lib.fp8w8a16_linear(x.data_ptr(), w.data_ptr(), scales.data_ptr(), _scale_dtype(scales), out.data_ptr(),
-                                 M, N, K, block_h, block_w, algo, ws.data_ptr(), ws.numel(), st)
+        if residual is not None:
+            _check_residual(residual, M, N, dev)
+            rc = lib.fp8w8a16_linear_residual(x.data_ptr(), w.data_ptr(), scales.data_ptr(), _scale_dtype(scales), residual.data_ptr(),
+                                              out.data_ptr(), M, N, K, block_h, block_w, ws.data_ptr(), ws.numel(), st)
+        else:
+            rc = lib.fp8w8a16_linear(x.data_ptr(), w.data_ptr(), scales.data_ptr(), _scale_dtype(scales), out.data_ptr(),
+                                     M, N, K, block_h, block_w, algo, ws.data_ptr(), ws.numel(), st)
         if rc:
             _cabi.check(rc, "fp8w8a16_linear")
     return out
+
+
+def add_rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float = 1e-6, residual: Optional[torch.Tensor] = None,
+                inplace_residual: bool = False) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """``z = x + residual`` (fp32 sum, one FP16 rounding; ``z = x`` without a residual), then
+    ``FP16(z * rsqrt(mean(z^2) + eps)) * weight``: the step vLLM's ``fused_add_rms_norm`` performs after a row-parallel
+    projection and its all-reduce.  Returns ``(normed, z)``; ``z`` is written into ``residual`` when ``inplace_residual``."""
+    dev = _require_cuda(x, weight)
+    if x.dtype != torch.float16 or x.dim() != 2 or weight.dtype != torch.float16 or weight.numel() != x.shape[1]:
+        raise RuntimeError(f"x must be float16 [M, N] and weight float16 [N] (got {tuple(x.shape)} {x.dtype}, {tuple(weight.shape)} {weight.dtype})")
+    M, N = x.shape
+    _check_residual(residual, M, N, dev)
+    out = torch.empty_like(x)
+    z = None
+    if residual is not None:
+        z = residual if inplace_residual else torch.empty_like(x)
+    with _dev_guard(dev):
+        _cabi.check(_cabi.load().fp8w8a16_add_rmsnorm(x.data_ptr(), None if residual is None else residual.data_ptr(), weight.data_ptr(),
+                                                       float(eps), out.data_ptr(), None if z is None else z.data_ptr(), M, N, _stream(dev)),
+                    "fp8w8a16_add_rmsnorm")
+    return out, (x if residual is None else z)
 
 
 class LinearPlan:
@@ -336,10 +372,12 @@ class PeerComm:
 
 
 def w8a16_linear_allreduce(comm: PeerComm, x: torch.Tensor, w: torch.Tensor, scales: torch.Tensor, N: int, K: int,
-                           block_h: int = 128, block_w: int = 128, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           block_h: int = 128, block_w: int = 128, out: Optional[torch.Tensor] = None,
+                           residual: Optional[torch.Tensor] = None) -> torch.Tensor:
     """This rank's K shard of a row-parallel linear, x [M, K_shard] @ dequant(w [N, K_shard])^T, summed over the ranks
     of ``comm`` inside the GEMM kernel: one launch replaces apply + all-reduce
-    (src/fp8_w8a16_sm70/vllm_serve.py:2922-2959).  The result is bit-identical on every rank."""
+    (src/fp8_w8a16_sm70/vllm_serve.py:2922-2959).  The result is bit-identical on every rank.  ``residual`` (float16
+    [M, N], the same values on every rank) joins the cross-rank sum before the one rounding."""
     w = _as_u8(w)
     dev = _require_cuda(x, w, scales)
     if x.dtype != torch.float16:
@@ -356,8 +394,10 @@ def w8a16_linear_allreduce(comm: PeerComm, x: torch.Tensor, w: torch.Tensor, sca
         if need is None:
             need = _LINEAR_WS_BYTES[(M, N, K)] = lib.fp8w8a16_linear_workspace_bytes(M, N, K)
         ws = workspace(dev, need, st)
-        rc = lib.fp8w8a16_linear_allreduce(comm._h, x.data_ptr(), w.data_ptr(), scales.data_ptr(), _scale_dtype(scales),
-                                           out.data_ptr(), M, N, K, block_h, block_w, ws.data_ptr(), ws.numel(), st)
+        _check_residual(residual, M, N, dev)
+        rc = lib.fp8w8a16_linear_allreduce_residual(comm._h, x.data_ptr(), w.data_ptr(), scales.data_ptr(), _scale_dtype(scales),
+                                                    None if residual is None else residual.data_ptr(), out.data_ptr(), M, N, K, block_h,
+                                                    block_w, ws.data_ptr(), ws.numel(), st)
         if rc:
             _cabi.check(rc, "fp8w8a16_linear_allreduce")
     return out

@@ -58,25 +58,33 @@ class TensorParallelLinear:
         assert mode in ("column", "row")
         self.w, self.s, self.block_h, self.mode, self.group = w_shard, s_shard, block_h, mode, group
         self.N, self.K = int(w_shard.shape[0]), int(w_shard.shape[1])
+        self._custom_linear = linear_fn
         self._linear = linear_fn or (lambda x: ops.w8a16_linear(x, self.w, self.s, self.N, self.K, self.block_h, 128))
         self.comm = comm if mode == "row" else None   # fused GEMM + all-reduce over peer memory
         # whether the LAYER has a bias: the same on every rank, unlike the bias argument of forward (rank 0 only)
         self.has_bias = bool(has_bias)
 
-    def forward(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         """column: x [M, K] (replicated) -> [M, N/tp].  row: x [M, K/tp] -> all-reduced [M, N]; the bias is
         added on rank 0 only before the reduce, as vLLM does.  The fused kernel is chosen from rank-invariant facts
-        only (token count, communicator size, ``has_bias``): a rank that went another way would leave its peers waiting."""
+        only (token count, communicator size, ``has_bias``): a rank that went another way would leave its peers waiting.
+        ``residual`` (row mode, float16 [M, N], replicated): the decoder's residual stream, added to the reduced result
+        with one rounding - inside the GEMM kernel on the fused paths."""
         if bias is not None and self.mode == "row" and self.comm is not None and not self.has_bias:
             raise RuntimeError("bias passed to a row-parallel layer built with has_bias=False: the ranks could not agree on the path")
         if self.comm is not None and not self.has_bias and x.shape[0] * self.N <= self.comm_max_elems():
-            return ops.w8a16_linear_allreduce(self.comm, x, self.w, self.s, self.N, self.K, self.block_h, 128)
+            return ops.w8a16_linear_allreduce(self.comm, x, self.w, self.s, self.N, self.K, self.block_h, 128, residual=residual)
+        world = dist.get_world_size(self.group) if dist.is_initialized() else 1
+        if residual is not None and self.mode == "row" and world == 1 and bias is None and self._custom_linear is None:
+            return ops.w8a16_linear(x, self.w, self.s, self.N, self.K, self.block_h, 128, residual=residual)
         y = self._linear(x)
         if self.mode == "row":
             if bias is not None and dist.get_rank(self.group) == 0:
                 y = y + bias.to(y.dtype)
-            if dist.is_initialized() and dist.get_world_size(self.group) > 1:
+            if world > 1:
                 dist.all_reduce(y, op=dist.ReduceOp.SUM, group=self.group)
+            if residual is not None:
+                y = (y.float() + residual.float()).to(y.dtype)
         elif bias is not None:
             y = y + bias.to(y.dtype)
         return y
