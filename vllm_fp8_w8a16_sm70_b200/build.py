@@ -15,7 +15,7 @@ PKG_DIR = Path(__file__).resolve().parent
 CSRC = PKG_DIR / "csrc"
 LIB_DIR = PKG_DIR / "lib"
 LIB_PATH = LIB_DIR / "libfp8w8a16_b200.so"
-SOURCES = ["capi.cu", "dequant.cu", "ep.cu", "gemv.cu", "gemm_tc.cu", "moe.cu", "noalloc.cu", "norm.cu"]
+SOURCES = ["capi.cu", "dequant.cu", "ep.cu", "gemv.cu", "gemm_tc.cu", "gemm_tc2.cu", "moe.cu", "noalloc.cu", "norm.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

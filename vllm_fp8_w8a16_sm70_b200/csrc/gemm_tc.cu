@@ -40,6 +40,7 @@
 
 #include "common.cuh"
 #include "gemm_tc.h"
+#include "tc_ptx.cuh"
 
 namespace w8a16 {
 
@@ -50,55 +51,6 @@ namespace {
 
 constexpr int kThreadsTc = 352;   // warp 0 TMA, warp 1 MMA, warps 2-9 dequant + epilogue, warp 10 second MMA issuer
 constexpr int kDequantThreads = 256;
-#ifdef W8A16_TIMEOUT_MS
-constexpr unsigned long long kTimeoutNs = (unsigned long long)(W8A16_TIMEOUT_MS) * 1000000ull;   // development builds
-#else
-constexpr unsigned long long kTimeoutNs = 2000000000ull;
-#endif
-
-// ---- PTX wrappers -----------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ unsigned long long globaltimer_ns() {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    return t;
-}
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok;
-}
-// Same, but the thread may be suspended by the hardware for up to `ns` while the phase is pending: a
-// waiting warp then costs no issue slots (the converting warps need them), and is woken when the phase flips.
-__device__ __forceinline__ uint32_t mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t ns) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity), "r"(ns)
-        : "memory");
-    return ok;
-}
-
 // Bounded wait.  Returns false when the CTA has been declared dead (by this or another thread).  `dead` points at
 // the CTA's flag words: [0] dead, [kReadyWord] "the kernel this launch depends on has finished".  Converting and MMA
 // warps start before that (see the dependency wait in the kernel): what they then wait for cannot happen until the
@@ -121,122 +73,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         }
     }
     return true;
-}
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0, int c1) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1)
-        : "memory");
-}
-
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
-__device__ __forceinline__ void tmem_alloc(uint32_t holder_smem, uint32_t ncols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder_smem), "r"(ncols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
-}
-
-// D[tmem] (+)= A[smem desc] * B[smem desc]^T, kind::f16, issued by one thread.
-__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Same with the A operand read from tensor memory (128 lanes x 8 columns per K = 16 step).
-__device__ __forceinline__ void umma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-// Accumulating form with a constant-true predicate: nothing but the MMA itself is issued.  The single
-// issuing thread is the narrowest point of the decode pipeline (a lone warp issues one instruction
-// every few cycles), so every instruction saved per MMA counts.
-__device__ __forceinline__ void umma_f16_ts_acc(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.eq.u32 p, 1, 1;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc)
-        : "memory");
-}
-// Eight 32-bit registers (16 FP16 values, K ascending, even K in the low half) -> eight consecutive
-// TMEM columns of this thread's lane.
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&r)[8]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};"
-                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7])
-                 : "memory");
-}
-__device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, float (&v)[8]) {
-    uint32_t r[8];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 bytes apart,
-// 8-row groups 1024 bytes apart (tile base 1024-byte aligned; K advances by adding bytes to the
-// start address inside the swizzle atom).
-__device__ __forceinline__ uint64_t make_desc_sw128(uint32_t saddr) {
-    uint64_t d = (uint64_t)((saddr & 0x3FFFFu) >> 4);  // start address, bits [0,14)
-    d |= (uint64_t)1 << 16;                            // leading byte offset (unused for swizzled K-major)
-    d |= (uint64_t)(1024u >> 4) << 32;                 // stride byte offset, bits [32,46)
-    d |= (uint64_t)1 << 46;                            // descriptor version (Blackwell)
-    d |= (uint64_t)2 << 61;                            // layout type: SWIZZLE_128B
-    return d;
-}
-
-// Instruction descriptor, kind::f16: D fp32, A and B FP16, both K-major, M = 128, N = n.
-__host__ __device__ constexpr uint32_t make_idesc_f16(int n) {
-    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(128 >> 4) << 24);
-}
-
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-    asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-__device__ __forceinline__ void epi_bar_sync() { asm volatile("bar.sync 1, 256;" ::: "memory"); }
-
-// Thread-block cluster helpers (synchronous split-K): every thread of every CTA of the cluster arrives and waits.
-__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release;" ::: "memory"); }
-__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire;" ::: "memory"); }
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire;" ::: "memory");
-}
-// Address of the same shared-memory location in the CTA of rank `rank` of this cluster.
-__device__ __forceinline__ uint32_t cluster_map(uint32_t local_saddr, uint32_t rank) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(local_saddr), "r"(rank));
-    return r;
-}
-__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
-    float4 v;
-    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
-    return v;
 }
 
 // Packets of the fused all-reduce: 16 bytes = two 8-byte halves {2 x FP16, epoch}; 8-byte accesses are single-copy
@@ -1355,6 +1191,11 @@ int max_active_clusters_for(int bt, bool paired, int cs) {
 
 }  // namespace
 
+int tc_encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t rows, uint64_t cols,
+                 uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz, bool is_weight) {
+    return encode_2d(map, dt, elem_bytes, base, rows, cols, box_rows, box_cols, swz, is_weight);
+}
+
 int tc_block_k(int bt, bool paired) { return (!paired && bt <= 64) ? 128 : 64; }
 
 int tc_ctas_per_sm(int bt, bool paired) { return (bt * (paired ? 2 : 1) <= 64) ? 2 : 1; }
@@ -1398,6 +1239,8 @@ int tc_pick_bt(int rows) {
 }
 
 int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st) {
+    // dense batches above 128 tokens: the CTA-pair kernel (gemm_tc2.cu)
+    if (bt == 256 && !paired && L.ar.world <= 1 && L.p.expert_offsets == nullptr && tc2_enabled()) return tc2_launch(L, st);
 #define W8A16_TC_CASE(BT_, BK_, P_) return launch_cfg<BT_, BK_, P_, false>(L, st)
 #define W8A16_TC_CASE_AR(BT_, BK_) return launch_cfg<BT_, BK_, false, true>(L, st)
     if (L.ar.world > 1) {
@@ -1432,13 +1275,15 @@ int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st) {
 
 
 int tc_read_status(int* out, int reset) {
-    int v = 0;
+    int v = 0, v2 = 0;
     W8A16_CUDA(cudaMemcpyFromSymbol(&v, g_tc_status, sizeof(int)));
     if (reset && v != 0) {
         const int zero = 0;
         W8A16_CUDA(cudaMemcpyToSymbol(g_tc_status, &zero, sizeof(int)));
     }
-    *out = v;
+    const int rc = tc2_read_status(&v2, reset);
+    if (rc) return rc;
+    *out = v | (v2 ? (v2 | 0x400) : 0);     // bit 0x400: the wait that ran out was in the CTA-pair kernel
     return 0;
 }
 

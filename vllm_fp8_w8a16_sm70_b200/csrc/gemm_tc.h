@@ -1,6 +1,7 @@
 // Launch parameters of the tcgen05 W8A16 GEMM (see gemm_tc.cu).
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -77,5 +78,12 @@ size_t tc_max_tiles_with_tickets();
 int tc_cluster_size(int64_t tiles, int total_kb, int bt, bool paired);
 int tc_launch(const TcLaunch& L, int bt, bool paired, cudaStream_t st);
 int tc_read_status(int* out, int reset);
+// 2-D row-major tensor map [rows, cols], box [box_rows, box_cols]; cached per (address, shape, box)
+int tc_encode_2d(CUtensorMap* map, CUtensorMapDataType dt, int elem_bytes, const void* base, uint64_t rows, uint64_t cols,
+                 uint32_t box_rows, uint32_t box_cols, CUtensorMapSwizzle swz, bool is_weight);
+// CTA-pair kernel for dense batches above 128 tokens (gemm_tc2.cu)
+bool tc2_enabled();
+int tc2_launch(const TcLaunch& L, cudaStream_t st);
+int tc2_read_status(int* out, int reset);
 
 }  // namespace w8a16
