@@ -76,6 +76,31 @@ def test_phase_ordered_ranks_match_the_single_gpu_layer(ops, P, scheme, I):
             e.close()
 
 
+def test_batches_on_both_sides_of_the_single_cta_limit(ops):
+    """Up to 16 routed rows one CTA builds the route table AND moves the rows (dispatch: stores into the peers' inboxes;
+    expert step: the gather of a small inbox); above that the table kernel is followed by one warp per row.  Ranks of one
+    call sit on both sides of the limit, and one call keeps every inbox small enough for the fused gather."""
+    E, H, topk, I, P = 16, 256, 4, 128, 4
+    base = make_moe(E, I, H, 1, topk, seed=9)
+    eps = _ranks(ops, P, 40, topk, H, E)
+    try:
+        for call, tokens in enumerate(([40, 16, 17, 3], [4, 2, 0, 1], [33, 33, 33, 33])):
+            batches = [make_moe(E, I, H, max(m, 1), topk, seed=300 + 10 * call + r, invalid_frac=0.1) for r, m in enumerate(tokens)]
+            for b, m in zip(batches, tokens):
+                for k in ("x", "tw", "ids"):
+                    b[k] = b[k][:m].contiguous()
+            outs = _call(ops, eps, base, batches, max(tokens))
+            for r, (b, m) in enumerate(zip(batches, tokens)):
+                assert tuple(outs[r].shape) == (m, H)
+                if m:
+                    omoe.check_moe(outs[r], omoe.moe_reference_fp32(b["x"], b["tw"], b["ids"], base["w13"], base["s13"], base["w2"],
+                                                                    base["s2"], base["bh"]))
+        assert ops.device_status() == 0
+    finally:
+        for e in eps:
+            e.close()
+
+
 def test_benchmark_shape_top8_of_128_experts(ops):
     """The MoE decode layer of the benchmark (128 experts, top-8, hidden 2048, intermediate 768) split over 8 ranks,
     8 tokens per rank."""

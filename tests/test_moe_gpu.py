@@ -71,7 +71,8 @@ def reference(d, ids=None):
 
 
 @pytest.mark.parametrize("E,I,H,M,topk", [(8, 256, 512, 1, 2), (8, 256, 512, 4, 2), (8, 256, 512, 33, 4), (16, 128, 256, 100, 4),
-                                           (4, 384, 1024, 300, 2), (128, 768, 2048, 2, 8)])
+                                           (4, 384, 1024, 300, 2), (128, 768, 2048, 2, 8),
+                                           (8, 256, 512, 4, 4), (8, 256, 512, 17, 1)])   # 16 and 17 routed rows: the two sides of the single-CTA gather limit
 def test_layer_block_scaled(ops, E, I, H, M, topk):
     d = make_moe(E, I, H, M, topk, seed=M)
     y = layer(ops, d)
@@ -148,7 +149,8 @@ def test_pieces_gather_grouped_combine(ops):
 
 
 @pytest.mark.parametrize("M,E,H,topk,dtype", [(1, 128, 2048, 8, torch.float16), (7, 128, 2048, 8, torch.bfloat16), (64, 60, 512, 4, torch.float32),
-                                              (3, 8, 64, 8, torch.float16), (33, 256, 1024, 6, torch.bfloat16)])
+                                              (3, 8, 64, 8, torch.float16), (33, 256, 1024, 6, torch.bfloat16),
+                                              (1003, 128, 1024, 8, torch.float16), (37, 24, 256, 2, torch.bfloat16)])   # past the cluster kernel's batch limit; few experts
 def test_router_gemv_topk_fused(ops, M, E, H, topk, dtype):
     """Gate GEMV + selection in one kernel.  The logits must match an fp32 matmul of the same tensors; given the
     kernel's own logits the picks must be EXACTLY the oracle's (indices bit-exact, ties to the lowest index)."""

@@ -8,6 +8,7 @@
 #include <new>
 
 #include "common.cuh"
+#include "align.cuh"
 #include "ep.h"
 #include "gemm_tc.h"
 
@@ -64,7 +65,9 @@ int launch_topk_softmax(const void* logits, int logits_dtype, int M, int E, int 
 int launch_router_topk(const __half* x, const void* gate, int gate_dtype, int M, int E, int H, int topk, int renorm, int shared_id,
                        float routed_scale, int* ids, float* weights, float* logits_out, cudaStream_t st);
 int launch_align(const void* ids, int ids_are_i64, int R, const int* expert_map, int n_global, int E, int bt, int* counts,
-                 int* offsets, int* tile_offsets, int* sorted_route, int* inv_pos, cudaStream_t st);
+                 int* offsets, int* tile_offsets, int* sorted_route, int* inv_pos, cudaStream_t st, const __half* x = nullptr,
+                 const float* topk_w = nullptr, int topk = 1, int H = 0, int weight_on_input = 0, __half* x_sorted = nullptr,
+                 float* w_sorted = nullptr);
 int launch_gather(const __half* x, const int* sorted_route, const float* topk_w, int R, int topk, int H, int weight_on_input,
                   __half* x_sorted, float* w_sorted, cudaStream_t st, const int* n_valid = nullptr, int pad_rows = 0);
 int launch_combine(const __half* y_sorted, const int* inv_pos, int M, int topk, int H, __half* out, cudaStream_t st);
@@ -275,7 +278,7 @@ struct Ep {
 // header must sit at the start of the workspace), then the receive lists, then the dispatch plan.
 struct EpLayout {
     MoeLayout moe;
-    size_t counts_in, ids_local, d_counts, d_offsets, d_tiles, d_sorted, d_inv, total;
+    size_t counts_in, d_counts, d_offsets, d_tiles, d_sorted, d_inv, total;
     int cap_call, rows_in;
 };
 
@@ -293,7 +296,6 @@ EpLayout ep_layout(const Ep& e, int M, int M_max, int E_local, int I) {
         return at;
     };
     L.counts_in = take(kEpMaxWorld * 4);
-    L.ids_local = take((size_t)L.rows_in * 4);
     const int R = M * e.topk;
     L.d_counts = take(kEpMaxWorld * 4);
     L.d_offsets = take((kEpMaxWorld + 1) * 4);
@@ -556,12 +558,20 @@ int fp8w8a16_moe_forward(const uint16_t* x, const void* topk_ids, int ids_are_i6
     __half* y_sorted = reinterpret_cast<__half*>(ws + L.y_sorted);
     cudaStream_t st = (cudaStream_t)stream;
 
-    int rc = launch_align(topk_ids, ids_are_i64, R, expert_map, n_global_experts, E, L.bt, counts, offsets, tile_offsets,
-                          sorted_route, inv_pos, st);
-    if (rc) return rc;
-    rc = launch_gather(reinterpret_cast<const __half*>(x), sorted_route, topk_weights, R, topk, H, weight_on_input, x_sorted,
-                       w_sorted, st);
-    if (rc) return rc;
+    int rc;
+    if (R <= kFuseRows) {
+        // few rows: the CTA that builds the route table gathers them too
+        rc = launch_align(topk_ids, ids_are_i64, R, expert_map, n_global_experts, E, L.bt, counts, offsets, tile_offsets, sorted_route,
+                          inv_pos, st, reinterpret_cast<const __half*>(x), topk_weights, topk, H, weight_on_input, x_sorted, w_sorted);
+        if (rc) return rc;
+    } else {
+        rc = launch_align(topk_ids, ids_are_i64, R, expert_map, n_global_experts, E, L.bt, counts, offsets, tile_offsets, sorted_route,
+                          inv_pos, st);
+        if (rc) return rc;
+        rc = launch_gather(reinterpret_cast<const __half*>(x), sorted_route, topk_weights, R, topk, H, weight_on_input, x_sorted,
+                           w_sorted, st);
+        if (rc) return rc;
+    }
     rc = grouped_gemm(x_sorted, w13, s13, scale_dtype, h_sorted, nullptr, offsets, tile_offsets, R, E, I, H, block_h, activation, L.bt,
                       ws + L.gemm_ws, L.gemm_ws_bytes, st);
     if (rc) return rc;
@@ -847,8 +857,13 @@ int fp8w8a16_ep_dispatch(fp8w8a16_ep* ep, const uint16_t* x, const void* topk_id
     const int R = M * e.topk;
     int* d_offsets = reinterpret_cast<int*>(ws + L.d_offsets);
     int* d_sorted = reinterpret_cast<int*>(ws + L.d_sorted);
+    const int* dest_map = reinterpret_cast<const int*>(e.g.base[e.g.rank] + e.off_dest_map);
+    if (R <= kFuseRows)   // few rows: route table, stores and headers in one launch
+        return launch_ep_send_small(reinterpret_cast<const __half*>(x), topk_ids, ids_are_i64, topk_weights, dest_map, e.n_global,
+                                    reinterpret_cast<int*>(ws + L.d_counts), d_offsets, reinterpret_cast<int*>(ws + L.d_tiles), d_sorted,
+                                    reinterpret_cast<int*>(ws + L.d_inv), R, e.topk, L.cap_call, e.g, st);
     // route table by destination rank: the align kernel with the expert -> rank map as its expert map
-    rc = launch_align(topk_ids, ids_are_i64, R, reinterpret_cast<const int*>(e.g.base[e.g.rank] + e.off_dest_map), e.n_global, e.g.world, 1,
+    rc = launch_align(topk_ids, ids_are_i64, R, dest_map, e.n_global, e.g.world, 1,
                       reinterpret_cast<int*>(ws + L.d_counts), d_offsets, reinterpret_cast<int*>(ws + L.d_tiles), d_sorted,
                       reinterpret_cast<int*>(ws + L.d_inv), st);
     if (rc) return rc;
@@ -878,7 +893,6 @@ int fp8w8a16_ep_experts(fp8w8a16_ep* ep, const uint8_t* w13, const void* s13, co
     cudaStream_t st = (cudaStream_t)stream;
     const MoeLayout& ML = L.moe;
     int* counts_in = reinterpret_cast<int*>(ws + L.counts_in);
-    int* ids_local = reinterpret_cast<int*>(ws + L.ids_local);
     int* counts = reinterpret_cast<int*>(ws + ML.counts);
     int* offsets = reinterpret_cast<int*>(ws + ML.offsets);
     int* tile_offsets = reinterpret_cast<int*>(ws + ML.tile_offsets);
@@ -890,14 +904,17 @@ int fp8w8a16_ep_experts(fp8w8a16_ep* ep, const uint8_t* w13, const void* s13, co
     __half* y_sorted = reinterpret_cast<__half*>(ws + ML.y_sorted);
     const char* mine = e.g.base[e.g.rank];
     const int Rin = L.rows_in;
-    rc = launch_ep_recv(L.cap_call, counts_in, ids_local, e.g, st);
+    // header wait and route table of the received rows in one launch; a small inbox is gathered by the same CTA
+    const int fuse_gather = Rin <= kFuseRows ? 1 : 0;
+    rc = launch_ep_recv_align(L.cap_call, counts_in, E, ML.bt, counts, offsets, tile_offsets, sorted_route, inv_pos, fuse_gather, x_sorted,
+                              w_sorted, e.g, st);
     if (rc) return rc;
-    rc = launch_align(ids_local, 0, Rin, nullptr, E, E, ML.bt, counts, offsets, tile_offsets, sorted_route, inv_pos, st);
-    if (rc) return rc;
-    // every received row is one route of its own (top-1 view of the inbox); its weight came with it
-    rc = launch_gather(reinterpret_cast<const __half*>(mine + e.g.off_rows), sorted_route, reinterpret_cast<const float*>(mine + e.g.off_meta_w),
-                       Rin, 1, H, 0, x_sorted, w_sorted, st, offsets + E, ML.bt);
-    if (rc) return rc;
+    if (!fuse_gather) {
+        // every received row is one route of its own (top-1 view of the inbox); its weight came with it
+        rc = launch_gather(reinterpret_cast<const __half*>(mine + e.g.off_rows), sorted_route,
+                           reinterpret_cast<const float*>(mine + e.g.off_meta_w), Rin, 1, H, 0, x_sorted, w_sorted, st, offsets + E, ML.bt);
+        if (rc) return rc;
+    }
     rc = grouped_gemm(x_sorted, w13, s13, scale_dtype, h_sorted, nullptr, offsets, tile_offsets, Rin, E, I, H, block_h, activation, ML.bt,
                       ws + ML.gemm_ws, ML.gemm_ws_bytes, st);
     if (rc) return rc;

@@ -7,10 +7,12 @@
 //   send     s: route table by DESTINATION rank (the align kernel with an expert -> rank map), then every routed row is
 //               stored straight into q's inbox region [s] (plain 16-byte peer stores) with its local expert id, its
 //               route index at the source and its route weight; when all rows of the grid have been stored, a header
-//               {count, call number} per destination follows (system-scope fence before it).
-//   receive  q: waits - bounded - for the header of every source, then lists the local expert id of every received
-//               row (-1 past a source's count); the ordinary grouped pipeline (align -> gather -> gate/up GEMM with the
-//               activation -> down GEMM x route weight) runs on those rows.
+//               {count, call number} per destination follows (system-scope fence before it).  Up to kFuseRows routed
+//               rows, one CTA does all of it in one launch.
+//   receive  q: ONE CTA waits - bounded - for the header of every source and sorts the received slots by local expert
+//               (a slot past its source's count is dropped; a small inbox is gathered into expert order by the same CTA);
+//               the ordinary grouped pipeline (gather -> gate/up GEMM with the activation -> down GEMM x route weight)
+//               runs on those rows.
 //   return   q: every finished row is stored into its source's return buffer at the row of its route index; a flag per
 //               source follows when all rows are stored.
 //   combine  s: waits - bounded - for the flag of every expert owner, then sums each token's routes in route order
@@ -21,6 +23,7 @@
 // The reference has no counterpart: it tolerates expert parallelism through expert_map and a later reduce
 // (src/fp8_w8a16_sm70/vllm_serve.py:2237-2243); the oracle of this path is the single-GPU layer.
 #include "common.cuh"
+#include "align.cuh"
 #include "ep.h"
 
 namespace w8a16 {
@@ -92,43 +95,49 @@ __device__ __forceinline__ int64_t read_id(const void* ids, int64_t i) {
     return (int64_t)reinterpret_cast<const T*>(ids)[i];
 }
 
-// ---- send: one warp per destination-sorted route ---------------------------------------------------------
+// ---- send ------------------------------------------------------------------------------------------------
+// One warp stores destination-sorted route `pos` (route index `route` at this rank) into its owner's inbox.
+__device__ __forceinline__ void send_row(const __half* __restrict__ x, const void* __restrict__ topk_ids, int ids_are_i64,
+                                         const float* __restrict__ topk_w, const int* dest_offsets, int pos, int route, int topk,
+                                         int cap_call, const EpGeom& g, int lane) {
+    const int H = g.H, P = g.world, s = g.rank;
+    int q = 0;
+    while (q + 1 < P && dest_offsets[q + 1] <= pos) ++q;     // at most 8 ranks
+    const int i = pos - dest_offsets[q];
+    if (i >= cap_call) return;
+    char* peer = g.base[q];
+    const int64_t slot = (int64_t)s * cap_call + i;
+    const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)(route / topk) * H);
+    uint4* dst = reinterpret_cast<uint4*>(peer + g.off_rows) + slot * (H >> 3);
+    const int vecs = H >> 3;
+    int v = lane;
+    for (; v + 96 < vecs; v += 128) {
+        const uint4 a = __ldg(src + v), b = __ldg(src + v + 32), c = __ldg(src + v + 64), d = __ldg(src + v + 96);
+        dst[v] = a;
+        dst[v + 32] = b;
+        dst[v + 64] = c;
+        dst[v + 96] = d;
+    }
+    for (; v < vecs; v += 32) dst[v] = __ldg(src + v);
+    if (lane == 0) {
+        const int64_t e = ids_are_i64 ? read_id<long long>(topk_ids, route) : read_id<int>(topk_ids, route);
+        reinterpret_cast<int*>(peer + g.off_meta_e)[slot] = (int)(e - (int64_t)q * g.experts_per_rank);
+        reinterpret_cast<int*>(peer + g.off_meta_j)[slot] = route;
+        reinterpret_cast<float*>(peer + g.off_meta_w)[slot] = topk_w[route];
+    }
+}
+
+// one warp per destination-sorted route; the route table comes from the align kernel
 __global__ void __launch_bounds__(256)
 k_ep_send(const __half* __restrict__ x, const void* __restrict__ topk_ids, int ids_are_i64, const float* __restrict__ topk_w,
           const int* __restrict__ sorted_route, const int* __restrict__ dest_offsets, int R, int topk, int cap_call, const EpGeom g) {
     pdl_trigger();
     pdl_wait();
     const uint32_t epoch = call_number(g);
-    const int H = g.H, P = g.world, s = g.rank;
+    const int P = g.world, s = g.rank;
     const int pos = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     const int route = pos < R ? sorted_route[pos] : -1;
-    if (route >= 0) {
-        int q = 0;
-        while (q + 1 < P && dest_offsets[q + 1] <= pos) ++q;     // at most 8 ranks
-        const int i = pos - dest_offsets[q];
-        if (i < cap_call) {
-            char* peer = g.base[q];
-            const int64_t slot = (int64_t)s * cap_call + i;
-            const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)(route / topk) * H);
-            uint4* dst = reinterpret_cast<uint4*>(peer + g.off_rows) + slot * (H >> 3);
-            const int vecs = H >> 3;
-            int v = lane;
-            for (; v + 96 < vecs; v += 128) {
-                const uint4 a = __ldg(src + v), b = __ldg(src + v + 32), c = __ldg(src + v + 64), d = __ldg(src + v + 96);
-                dst[v] = a;
-                dst[v + 32] = b;
-                dst[v + 64] = c;
-                dst[v + 96] = d;
-            }
-            for (; v < vecs; v += 32) dst[v] = __ldg(src + v);
-            if (lane == 0) {
-                const int64_t e = ids_are_i64 ? read_id<long long>(topk_ids, route) : read_id<int>(topk_ids, route);
-                reinterpret_cast<int*>(peer + g.off_meta_e)[slot] = (int)(e - (int64_t)q * g.experts_per_rank);
-                reinterpret_cast<int*>(peer + g.off_meta_j)[slot] = route;
-                reinterpret_cast<float*>(peer + g.off_meta_w)[slot] = topk_w[route];
-            }
-        }
-    }
+    if (route >= 0) send_row(x, topk_ids, ids_are_i64, topk_w, dest_offsets, pos, route, topk, cap_call, g, lane);
     grid_done_then(ctrl_word(g, 1), [&]() {
         if ((int)threadIdx.x < P) {
             const int q = threadIdx.x;
@@ -139,13 +148,53 @@ k_ep_send(const __half* __restrict__ x, const void* __restrict__ topk_ids, int i
     });
 }
 
-// ---- receive: headers -> per-source counts and the local expert id of every slot --------------------------------
-__global__ void __launch_bounds__(1024)
-k_ep_recv(int cap_call, int* __restrict__ counts_in, int* __restrict__ ids_local, const EpGeom g) {
+// Small batches: ONE CTA builds the route table by destination rank (align.cuh, key = owner of the route's expert), stores
+// the rows and publishes the headers - one launch instead of two.
+template <typename IdT>
+__global__ void __launch_bounds__(kAlignThreads)
+k_ep_send_small(const __half* __restrict__ x, const IdT* __restrict__ topk_ids, const float* __restrict__ topk_w,
+                const int* __restrict__ dest_map, int n_global, int* __restrict__ counts, int* __restrict__ offsets,
+                int* __restrict__ tile_offsets, int* __restrict__ sorted_route, int* __restrict__ inv_pos, int R, int topk,
+                int cap_call, const EpGeom g) {
     pdl_trigger();
+    extern __shared__ int sm[];
+    const int P = g.world, s = g.rank;
+    for (int i = threadIdx.x; i < kAlignWarps * P; i += kAlignThreads) sm[i] = 0;
+    pdl_wait();
+    __syncthreads();
+    align_core([&](int i) { return local_expert(topk_ids, i, dest_map, n_global, P); }, R, P, 1, counts, offsets, tile_offsets,
+               sorted_route, inv_pos, sm);
+    __syncthreads();   // sorted_route and the offsets are complete
+    const uint32_t epoch = call_number(g);
+    const int* s_off = sm + kAlignWarps * P;   // exclusive row offsets per destination, [P] = number of valid rows
+    const int n_valid = s_off[P];
+    for (int pos = threadIdx.x >> 5; pos < n_valid; pos += kAlignWarps)
+        send_row(x, topk_ids, sizeof(IdT) == 8, topk_w, s_off, pos, sorted_route[pos], topk, cap_call, g, threadIdx.x & 31);
+    __threadfence_system();   // every thread's peer stores before the CTA-wide barrier ...
+    __syncthreads();
+    if ((int)threadIdx.x < P) {
+        __threadfence_system();   // ... and all of them before this thread's header
+        const int q = threadIdx.x;
+        int cnt = s_off[q + 1] - s_off[q];
+        if (cnt > cap_call) cnt = cap_call;
+        st_flag(reinterpret_cast<uint2*>(g.base[q] + g.off_hdr) + s, (uint32_t)cnt, epoch);
+    }
+}
+
+// ---- receive -------------------------------------------------------------------------------------------
+// Receive and local route table in ONE CTA: waits for the headers, then sorts the received slots by local expert
+// (align.cuh; a slot past its source's count, or with an expert id out of range, is dropped) and - for small inboxes -
+// gathers the rows into expert order too, so that the separate receive, align and gather launches are not needed.
+__global__ void __launch_bounds__(kAlignThreads)
+k_ep_recv_align(int cap_call, int* __restrict__ counts_in, int E, int bt, int* __restrict__ counts, int* __restrict__ offsets,
+                int* __restrict__ tile_offsets, int* __restrict__ sorted_route, int* __restrict__ inv_pos, int fuse_gather,
+                __half* __restrict__ x_sorted, float* __restrict__ w_sorted, const EpGeom g) {
+    pdl_trigger();
+    extern __shared__ int sm[];
+    int* s_cnt = sm + kAlignWarps * E + E + 1;   // [kEpMaxWorld]
+    for (int i = threadIdx.x; i < kAlignWarps * E; i += kAlignThreads) sm[i] = 0;
     pdl_wait();
     const uint32_t epoch = call_number(g);
-    __shared__ int s_cnt[kEpMaxWorld];
     const char* mine = g.base[g.rank];
     if ((int)threadIdx.x < g.world) {
         const int c = wait_flag(reinterpret_cast<const uint2*>(mine + g.off_hdr) + threadIdx.x, epoch,
@@ -156,14 +205,23 @@ k_ep_recv(int cap_call, int* __restrict__ counts_in, int* __restrict__ ids_local
     __syncthreads();
     const int* meta_e = reinterpret_cast<const int*>(mine + g.off_meta_e);
     const int total = g.world * cap_call;
-    for (int idx = blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += gridDim.x * blockDim.x) {
-        const int s = idx / cap_call, i = idx - s * cap_call;
-        int e = -1;
-        if (i < s_cnt[s]) {
-            e = __ldcg(meta_e + idx);
-            if (e < 0 || e >= g.experts_per_rank) e = -1;
-        }
-        ids_local[idx] = e;
+    const int n_valid = align_core(
+        [&](int idx) {
+            const int s = idx / cap_call, i = idx - s * cap_call;
+            if (i >= s_cnt[s]) return -1;
+            const int e = __ldcg(meta_e + idx);
+            return (e < 0 || e >= E) ? -1 : e;
+        },
+        total, E, bt, counts, offsets, tile_offsets, sorted_route, inv_pos, sm);
+    if (fuse_gather) {
+        __syncthreads();   // sorted_route is complete
+        // every received row is one route of its own (top-1 view of the inbox); rows up to the end of the last token tile
+        // are zero-filled
+        const int rows = min(total, n_valid + bt);
+        const __half* rows_in = reinterpret_cast<const __half*>(mine + g.off_rows);
+        const float* w_in = reinterpret_cast<const float*>(mine + g.off_meta_w);
+        for (int pos = threadIdx.x >> 5; pos < rows; pos += kAlignWarps)
+            gather_row(rows_in, sorted_route[pos], w_in, 1, g.H, 0, x_sorted, w_sorted, pos, threadIdx.x & 31);
     }
 }
 
@@ -292,8 +350,33 @@ int launch_ep_send(const __half* x, const void* topk_ids, int ids_are_i64, const
                                     R, topk, cap_call, g), "ep_send");
 }
 
-int launch_ep_recv(int cap_call, int* counts_in, int* ids_local, const EpGeom& g, cudaStream_t st) {
-    return finish_launch(launch_pdl(k_ep_recv, dim3(1), dim3(1024), 0, st, cap_call, counts_in, ids_local, g), "ep_recv");
+int launch_ep_send_small(const __half* x, const void* topk_ids, int ids_are_i64, const float* topk_w, const int* dest_map, int n_global,
+                         int* counts, int* offsets, int* tile_offsets, int* sorted_route, int* inv_pos, int R, int topk, int cap_call,
+                         const EpGeom& g, cudaStream_t st) {
+    const size_t smem = align_smem_bytes(g.world);
+    cudaError_t le;
+    if (ids_are_i64)
+        le = launch_pdl(k_ep_send_small<long long>, dim3(1), dim3(kAlignThreads), smem, st, x, reinterpret_cast<const long long*>(topk_ids),
+                        topk_w, dest_map, n_global, counts, offsets, tile_offsets, sorted_route, inv_pos, R, topk, cap_call, g);
+    else
+        le = launch_pdl(k_ep_send_small<int>, dim3(1), dim3(kAlignThreads), smem, st, x, reinterpret_cast<const int*>(topk_ids), topk_w,
+                        dest_map, n_global, counts, offsets, tile_offsets, sorted_route, inv_pos, R, topk, cap_call, g);
+    return finish_launch(le, "ep_send_small");
+}
+
+int launch_ep_recv_align(int cap_call, int* counts_in, int E, int bt, int* counts, int* offsets, int* tile_offsets, int* sorted_route,
+                         int* inv_pos, int fuse_gather, __half* x_sorted, float* w_sorted, const EpGeom& g, cudaStream_t st) {
+    W8A16_REQUIRE(E >= 1 && E <= 1024, FP8W8A16_ERR_UNSUPPORTED, "ep_recv_align: E=%d out of range [1,1024]", E);
+    const size_t smem = align_smem_bytes(E) + kEpMaxWorld * sizeof(int);
+    static int set_bytes[64] = {};
+    int dev = 0;
+    W8A16_CUDA(cudaGetDevice(&dev));
+    if (smem > 48 * 1024 && (dev < 0 || dev >= 64 || (int)smem > set_bytes[dev])) {
+        W8A16_CUDA(cudaFuncSetAttribute(k_ep_recv_align, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (dev >= 0 && dev < 64) set_bytes[dev] = (int)smem;
+    }
+    return finish_launch(launch_pdl(k_ep_recv_align, dim3(1), dim3(kAlignThreads), smem, st, cap_call, counts_in, E, bt, counts, offsets,
+                                    tile_offsets, sorted_route, inv_pos, fuse_gather, x_sorted, w_sorted, g), "ep_recv_align");
 }
 
 int launch_ep_return(const __half* y_sorted, const int* inv_pos, const int* counts_in, int cap_call, const EpGeom& g, cudaStream_t st) {

@@ -29,7 +29,13 @@ struct EpGeom {
 
 int launch_ep_send(const __half* x, const void* topk_ids, int ids_are_i64, const float* topk_w, const int* sorted_route,
                    const int* dest_offsets, int R, int topk, int cap_call, const EpGeom& g, cudaStream_t st);
-int launch_ep_recv(int cap_call, int* counts_in, int* ids_local, const EpGeom& g, cudaStream_t st);
+// small batches: route table by destination, stores and headers in one launch (replaces the align kernel + launch_ep_send)
+int launch_ep_send_small(const __half* x, const void* topk_ids, int ids_are_i64, const float* topk_w, const int* dest_map, int n_global,
+                         int* counts, int* offsets, int* tile_offsets, int* sorted_route, int* inv_pos, int R, int topk, int cap_call,
+                         const EpGeom& g, cudaStream_t st);
+// header wait + route table of the received rows by local expert (+ the gather into expert order when fuse_gather is set)
+int launch_ep_recv_align(int cap_call, int* counts_in, int E, int bt, int* counts, int* offsets, int* tile_offsets, int* sorted_route,
+                         int* inv_pos, int fuse_gather, __half* x_sorted, float* w_sorted, const EpGeom& g, cudaStream_t st);
 int launch_ep_return(const __half* y_sorted, const int* inv_pos, const int* counts_in, int cap_call, const EpGeom& g, cudaStream_t st);
 int launch_ep_combine(const void* topk_ids, int ids_are_i64, int M, int topk, __half* out, const EpGeom& g, cudaStream_t st);
 int ep_read_status(int* out, int reset);

@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 
 #include "common.cuh"
+#include "align.cuh"
 
 namespace w8a16 {
 
@@ -229,113 +230,27 @@ __global__ void __launch_bounds__(256) k_router_topk_cluster(const __half* __res
 }
 
 // ------------------------------------------------------------------------------------------------
-// align: one CTA.  Stable counting sort of the routed rows by local expert id.
+// align: one CTA.  Stable counting sort of the routed rows by local expert id (align.cuh).  With `x` given (small
+// problems) the same CTA then gathers the rows, one warp per sorted position, and the gather kernel is not launched.
 // ------------------------------------------------------------------------------------------------
-constexpr int kAlignThreads = 1024;
-constexpr int kAlignWarps = kAlignThreads / 32;
-
-template <typename IdT>
-__device__ __forceinline__ int local_expert(const IdT* ids, int i, const int* expert_map, int n_global, int E) {
-    long long g = (long long)ids[i];
-    if (g < 0) return -1;
-    if (expert_map != nullptr) {
-        if (g >= n_global) return -1;
-        g = expert_map[g];
-    }
-    return (g >= 0 && g < E) ? (int)g : -1;
-}
-
 template <typename IdT>
 __global__ void __launch_bounds__(kAlignThreads)
 k_align(const IdT* __restrict__ ids, int R, const int* __restrict__ expert_map, int n_global, int E, int bt,
         int* __restrict__ counts, int* __restrict__ offsets, int* __restrict__ tile_offsets,
-        int* __restrict__ sorted_route, int* __restrict__ inv_pos) {
+        int* __restrict__ sorted_route, int* __restrict__ inv_pos, const __half* __restrict__ x, const float* __restrict__ topk_w,
+        int topk, int H, int weight_on_input, __half* __restrict__ x_sorted, float* __restrict__ w_sorted) {
     pdl_trigger();
     extern __shared__ int sm[];
-    int* warp_hist = sm;                       // [kAlignWarps][E] -> later: running placement cursor
-    int* s_off = sm + kAlignWarps * E;         // [E + 1]
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    for (int i = tid; i < kAlignWarps * E; i += kAlignThreads) warp_hist[i] = 0;
+    for (int i = threadIdx.x; i < kAlignWarps * E; i += kAlignThreads) sm[i] = 0;
     pdl_wait();   // the expert ids come from the previous kernel
     __syncthreads();
-
-    // contiguous segment of routes per warp, walked in order 32 at a time
-    const int per_warp = ((R + kAlignWarps - 1) / kAlignWarps + 31) & ~31;
-    const int seg_begin = min(R, warp * per_warp), seg_end = min(R, seg_begin + per_warp);
-    for (int base = seg_begin; base < seg_end; base += 32) {
-        const int i = base + lane;
-        const int e = i < seg_end ? local_expert(ids, i, expert_map, n_global, E) : -1;
-        if (e >= 0) atomicAdd(&warp_hist[warp * E + e], 1);
+    align_core([&](int i) { return local_expert(ids, i, expert_map, n_global, E); }, R, E, bt, counts, offsets, tile_offsets,
+               sorted_route, inv_pos, sm);
+    if (x != nullptr) {
+        __syncthreads();   // sorted_route is complete
+        for (int pos = threadIdx.x >> 5; pos < R; pos += kAlignWarps)
+            gather_row(x, sorted_route[pos], topk_w, topk, H, weight_on_input, x_sorted, w_sorted, pos, threadIdx.x & 31);
     }
-    __syncthreads();
-    // per expert: total count; turn per-warp counts into exclusive prefix over warps
-    for (int e = tid; e < E; e += kAlignThreads) {
-        int run = 0;
-        for (int w = 0; w < kAlignWarps; ++w) {
-            const int c = warp_hist[w * E + e];
-            warp_hist[w * E + e] = run;
-            run += c;
-        }
-        counts[e] = run;
-        s_off[e] = run;  // counts for now
-    }
-    __syncthreads();
-    if (warp == 0) {
-        // exclusive scan of the counts (rows) and of ceil(count / bt) (token tiles) by one warp: every
-        // lane scans a contiguous run of experts, the lane totals are scanned with shuffles
-        const int per_lane = (E + 31) / 32;
-        const int e0 = lane * per_lane, e1 = min(E, e0 + per_lane);
-        int rows = 0, tiles = 0;
-        for (int e = e0; e < e1; ++e) {
-            const int c = s_off[e];
-            rows += c;
-            tiles += (c + bt - 1) / bt;
-        }
-        int rows_incl = rows, tiles_incl = tiles;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int a = __shfl_up_sync(0xFFFFFFFFu, rows_incl, o);
-            const int b = __shfl_up_sync(0xFFFFFFFFu, tiles_incl, o);
-            if (lane >= o) {
-                rows_incl += a;
-                tiles_incl += b;
-            }
-        }
-        int run = rows_incl - rows, trun = tiles_incl - tiles;
-        for (int e = e0; e < e1; ++e) {
-            const int c = s_off[e];
-            s_off[e] = run;
-            offsets[e] = run;
-            tile_offsets[e] = trun;
-            run += c;
-            trun += (c + bt - 1) / bt;
-        }
-        if (lane == 31) {
-            s_off[E] = rows_incl;
-            offsets[E] = rows_incl;
-            tile_offsets[E] = tiles_incl;
-        }
-    }
-    __syncthreads();
-    const int n_valid = s_off[E];
-    for (int base = seg_begin; base < seg_end; base += 32) {
-        const int i = base + lane;
-        const int e = i < seg_end ? local_expert(ids, i, expert_map, n_global, E) : -1;
-        const unsigned peers = __match_any_sync(0xFFFFFFFFu, e);
-        if (e >= 0) {
-            const int rank = __popc(peers & ((1u << lane) - 1u));
-            const int cur = warp_hist[warp * E + e];
-            const int pos = s_off[e] + cur + rank;
-            sorted_route[pos] = i;
-            inv_pos[i] = pos;
-            __syncwarp(peers);
-            if (rank == 0) warp_hist[warp * E + e] = cur + __popc(peers);
-        } else if (i < seg_end) {
-            inv_pos[i] = -1;
-        }
-        __syncwarp();
-    }
-    for (int i = n_valid + tid; i < R; i += kAlignThreads) sorted_route[i] = -1;
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -354,40 +269,7 @@ k_gather(const __half* __restrict__ x, const int* __restrict__ sorted_route, con
     const int pos = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (pos >= R) return;
     if (n_valid != nullptr && pos >= *n_valid + pad_rows) return;
-    const int route = sorted_route[pos];
-    uint4* dst = reinterpret_cast<uint4*>(x_sorted + (int64_t)pos * H);
-    const int vecs = H >> 3;
-    if (route < 0) {
-        for (int i = lane; i < vecs; i += 32) dst[i] = make_uint4(0, 0, 0, 0);
-        if (lane == 0) w_sorted[pos] = 0.f;
-        return;
-    }
-    const float wt = topk_w[route];
-    const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)(route / topk) * H);
-    if (!weight_on_input) {
-        int i = lane;
-        for (; i + 96 < vecs; i += 128) {   // four 16-byte loads in flight per lane
-            const uint4 a = __ldg(src + i), b = __ldg(src + i + 32), c = __ldg(src + i + 64), d = __ldg(src + i + 96);
-            dst[i] = a;
-            dst[i + 32] = b;
-            dst[i + 64] = c;
-            dst[i + 96] = d;
-        }
-        for (; i < vecs; i += 32) dst[i] = __ldg(src + i);
-        if (lane == 0) w_sorted[pos] = wt;
-    } else {
-        // reference: route_x * route_w.unsqueeze(-1) on FP16 tensors (vllm_serve.py:1868-1870)
-        const __half w16 = __float2half_rn(wt);
-        const __half2 w2 = __halves2half2(w16, w16);
-        for (int i = lane; i < vecs; i += 32) {
-            uint4 v = __ldg(src + i);
-            __half2* h = reinterpret_cast<__half2*>(&v);
-#pragma unroll
-            for (int j = 0; j < 4; ++j) h[j] = __hmul2(h[j], w2);
-            dst[i] = v;
-        }
-        if (lane == 0) w_sorted[pos] = 1.f;
-    }
+    gather_row(x, sorted_route[pos], topk_w, topk, H, weight_on_input, x_sorted, w_sorted, pos, lane);
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -523,10 +405,14 @@ int launch_router_topk(const __half* x, const void* gate, int gate_dtype, int M,
     return fail(FP8W8A16_ERR_INVALID, "moe_router_topk: unknown gate weight dtype %d", gate_dtype);
 }
 
+// With `x` given the align CTA also gathers the rows (callers do that for R <= kFuseRows and then skip launch_gather).
 int launch_align(const void* ids, int ids_are_i64, int R, const int* expert_map, int n_global, int E, int bt, int* counts,
-                 int* offsets, int* tile_offsets, int* sorted_route, int* inv_pos, cudaStream_t st) {
+                 int* offsets, int* tile_offsets, int* sorted_route, int* inv_pos, cudaStream_t st, const __half* x,
+                 const float* topk_w, int topk, int H, int weight_on_input, __half* x_sorted, float* w_sorted) {
     W8A16_REQUIRE(E >= 1 && E <= 1024, FP8W8A16_ERR_UNSUPPORTED, "moe_align: E=%d out of range [1,1024]", E);
-    const size_t smem = ((size_t)kAlignWarps * E + E + 1) * sizeof(int);
+    W8A16_REQUIRE(x == nullptr || (H % 8 == 0 && topk >= 1 && topk_w && x_sorted && w_sorted), FP8W8A16_ERR_INVALID,
+                  "moe_align: fused gather needs H %% 8 == 0 (got %d), topk >= 1 and the gather buffers", H);
+    const size_t smem = align_smem_bytes(E);
     // Above 48 KiB (E > ~370) the kernel's dynamic shared-memory limit has to be raised.  The attribute belongs to the
     // (function, device) pair and a later call may need more than an earlier one: remember the largest value set per device.
     static int set_bytes[2][64] = {};
@@ -541,10 +427,12 @@ int launch_align(const void* ids, int ids_are_i64, int R, const int* expert_map,
     cudaError_t le;
     if (ids_are_i64)
         le = launch_pdl(k_align<long long>, dim3(1), dim3(kAlignThreads), smem, st, reinterpret_cast<const long long*>(ids), R, expert_map,
-                        n_global, E, bt, counts, offsets, tile_offsets, sorted_route, inv_pos);
+                        n_global, E, bt, counts, offsets, tile_offsets, sorted_route, inv_pos, x, topk_w, topk, H, weight_on_input,
+                        x_sorted, w_sorted);
     else
         le = launch_pdl(k_align<int>, dim3(1), dim3(kAlignThreads), smem, st, reinterpret_cast<const int*>(ids), R, expert_map, n_global,
-                        E, bt, counts, offsets, tile_offsets, sorted_route, inv_pos);
+                        E, bt, counts, offsets, tile_offsets, sorted_route, inv_pos, x, topk_w, topk, H, weight_on_input, x_sorted,
+                        w_sorted);
     return finish_launch(le, "moe_align");
 }
 
