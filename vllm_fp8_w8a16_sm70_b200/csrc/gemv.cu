@@ -185,18 +185,37 @@ int resident_ctas_per_sm(int m) {
 
 }  // namespace
 
-// Number of K splits for a GEMV over [N,K]: about four units per resident warp for balance, every unit at
-// least two double steps (2048 elements) long.
-int gemv_pick_splits(int N, int K) {
+// K range of one unit for a GEMV over [N,K] (a multiple of the 512-element step; the number of splits follows from it).
+// All units are the same size and the warps of the resident grid take them in waves, so a launch lasts about
+// ceil(units / warps) * k_chunk elements per warp: the candidate with the smallest such product wins (every unit at least
+// 2048 elements long; a split costs a partial-sum round trip, so ties go to fewer splits).
+int gemv_pick_chunk(int N, int K) {
     const int row_groups = (N + kRows - 1) / kRows;
-    if (row_groups > kMaxTicketGroups) return 1;   // more row groups than ticket counters: already plenty of units
-    const int want_units = gemv_grid_ctas() * kWarps * 4;
-    int s = want_units / row_groups;   // no split when the row groups alone give enough units
-    const int max_s = (K / (4 * kStep)) > 0 ? K / (4 * kStep) : 1;
-    if (s > max_s) s = max_s;
-    if (s > 32) s = 32;
-    if (s < 1) s = 1;
-    return s;
+    const int k_full = (K + kStep - 1) / kStep * kStep;
+    if (row_groups > kMaxTicketGroups) return k_full;   // more row groups than ticket counters: no split (already plenty of units)
+    const int64_t warps = (int64_t)gemv_grid_ctas() * kWarps;
+    int max_s = K / (4 * kStep);
+    if (max_s > 32) max_s = 32;
+    if (max_s < 1) max_s = 1;
+    int best_chunk = k_full;
+    int64_t best_cost = -1;
+    for (int s = 1; s <= max_s; ++s) {
+        const int chunk = ((K + s - 1) / s + kStep - 1) / kStep * kStep;
+        const int splits = (K + chunk - 1) / chunk;
+        const int64_t units = (int64_t)row_groups * splits;
+        const int64_t waves = (units + warps - 1) / warps;
+        const int64_t cost = waves * chunk + (splits > 1 ? 64 * splits : 0);
+        if (best_cost < 0 || cost < best_cost) {
+            best_cost = cost;
+            best_chunk = chunk;
+        }
+    }
+    return best_chunk;
+}
+
+int gemv_pick_splits(int N, int K) {
+    const int chunk = gemv_pick_chunk(N, K);
+    return (K + chunk - 1) / chunk;
 }
 
 size_t gemv_workspace_bytes(int M, int N, int K) {
@@ -216,9 +235,8 @@ int launch_gemv(const __half* x, const uint8_t* w, const void* scales, int scale
     if (M == 0 || N == 0) return 0;
     const int Kb = (K + 127) / 128;
     const int row_groups = (N + kRows - 1) / kRows;
-    int splits = gemv_pick_splits(N, K);
-    int k_chunk = ((K + splits - 1) / splits + 2 * kStep - 1) / (2 * kStep) * (2 * kStep);
-    splits = (K + k_chunk - 1) / k_chunk;
+    const int k_chunk = gemv_pick_chunk(N, K);
+    const int splits = (K + k_chunk - 1) / k_chunk;
     float* partial = nullptr;
     unsigned int* tickets = nullptr;
     if (splits > 1) {
