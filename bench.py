@@ -124,6 +124,11 @@ def dist_setup(n_gpus: int):
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
         import torch.distributed as dist
+        # Collectives captured in CUDA graphs work on graph-private buffers that die with their graph; the per-case
+        # timing creates and destroys a graph per case.  With NCCL's registration of captured buffers left on, the 14th
+        # such graph of a run faulted on this pool (2 and 4 GPUs, "unspecified launch failure"; the same case alone ran
+        # clean), so captured buffers are not registered here and the per-case graphs are kept until the run ends.
+        os.environ.setdefault("NCCL_GRAPH_REGISTER", "0")
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     else:
@@ -382,6 +387,7 @@ def run_dense(args, world, rank, local, m_list, workload: str) -> dict:
 
     # ---- per-case device times (rank-local) for the roofline: every case cycles over its weight copies ----
     cases = []
+    kept_graphs = []
     reps = 6 if workload == "decode" else 2
     flush = Flusher(device)
     for M in m_list:
@@ -398,6 +404,8 @@ def run_dense(args, world, rank, local, m_list, workload: str) -> dict:
                 b.record()
                 b.synchronize()
                 ms = a.elapsed_time(b) / (reps * len(lst))
+                if world > 1:
+                    kept_graphs.append(g)     # graphs that hold collectives live until the run ends (see dist_setup)
                 del g
             else:
                 ms = time_call(lambda: lst[0].forward(xs[M][name]), reps, flush)
