@@ -126,7 +126,7 @@ def dist_setup(n_gpus: int):
         import torch.distributed as dist
         # Collectives captured in CUDA graphs work on graph-private buffers that die with their graph; the per-case
         # timing creates and destroys a graph per case.  With NCCL's registration of captured buffers left on, the 14th
-        # such graph of a run faulted on this pool (2 and 4 GPUs, "unspecified launch failure"; the same case alone ran
+        # such graph of a run faulted on B200 with NCCL 2.28 (2 and 4 GPUs, "unspecified launch failure"; the same case alone ran
         # clean), so captured buffers are not registered here and the per-case graphs are kept until the run ends.
         os.environ.setdefault("NCCL_GRAPH_REGISTER", "0")
         torch.cuda.set_device(local)
