@@ -40,7 +40,6 @@ __device__ int g_tc2_status = 0;   // sticky error bits of this kernel's bounded
 namespace {
 
 constexpr int kThreads2 = 320;
-constexpr int kConv = 256;            // converting threads (warps 2-9)
 constexpr int kBT = 256;              // tokens per pair tile (128 staged by each CTA)
 constexpr int kBK = 128;              // K block
 constexpr int kNS = 4;                // stages: raw ring, activation ring and operand ring share the index
