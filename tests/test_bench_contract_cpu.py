@@ -36,3 +36,23 @@ def test_gpu_arm_refuses_to_run_without_a_gpu():
                        timeout=300, cwd=str(ROOT))
     assert p.returncode != 0
     assert "no CPU path" in (p.stderr + p.stdout)
+
+
+def test_traffic_figure_follows_the_kernel_source(monkeypatch, tmp_path):
+    """roofline.traffic comes from the figures file beside the committed ncu summary and is only reported while the
+    kernel source is the one it was captured on.  The committed pair must be in step (else the bench line would carry
+    null), and a changed source must demote the figure to `traffic_stale`."""
+    sys.path.insert(0, str(ROOT))
+    import bench
+    got = bench.capture_traffic()
+    assert got["traffic"] is not None and got["traffic"] >= got["traffic_algorithmic_bytes"] > 0, got
+    assert got["traffic"] < 1.2 * got["traffic_algorithmic_bytes"], "DRAM traffic far above the algorithmic bytes means re-reads"
+    # same figures, different source: stale
+    fake = tmp_path / "repo"
+    (fake / "profiles").mkdir(parents=True)
+    (fake / "vllm_fp8_w8a16_sm70_b200" / "csrc").mkdir(parents=True)
+    (fake / "profiles" / "k_gemm_tc_decode_gate_up_m16.json").write_text((ROOT / "profiles" / "k_gemm_tc_decode_gate_up_m16.json").read_text())
+    (fake / "vllm_fp8_w8a16_sm70_b200" / "csrc" / "gemm_tc.cu").write_text("// something else\n")
+    monkeypatch.setattr(bench, "ROOT", fake)
+    stale = bench.capture_traffic()
+    assert stale["traffic"] is None and stale["traffic_stale"] == got["traffic"] and "changed" in stale["traffic_note"]
